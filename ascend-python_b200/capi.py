@@ -1,0 +1,183 @@
+"""ctypes binding of the C ABI declared in ``include/qmm_b200.h``.
+
+This is the thinnest possible host: it passes raw device pointers taken from
+torch tensors to ``libqmm_b200.so``.  The torch custom ops (``op_plugin``) are
+the production host; this module exists for tests, benchmarks and for callers
+that have no torch dispatcher.  There is no fallback: if the library is not
+built, loading raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+import torch
+
+_PKG = Path(__file__).resolve().parent
+LIB_PATH = _PKG / "lib" / "libqmm_b200.so"
+
+QMM_OK = 0
+DTYPE_BF16, DTYPE_F16, DTYPE_F32, DTYPE_I32, DTYPE_NONE = 0, 1, 2, 3, -1
+ALGO_AUTO, ALGO_TILE, ALGO_STREAMK, ALGO_SIMT = 0, 1, 2, 3
+UNIQUE_ID_BYTES = 128
+
+# every symbol include/qmm_b200.h declares
+EXPORTED_SYMBOLS = (
+    "qmm_last_error", "qmm_version", "qmm_device_status", "qmm_dynamic_quant",
+    "qmm_quant_matmul_workspace_size", "qmm_quant_matmul", "qmm_weight_quant_batchmatmul",
+    "qmm_comm_unique_id", "qmm_comm_init_rank", "qmm_comm_register", "qmm_comm_info", "qmm_comm_destroy",
+    "qmm_mm_all_reduce",
+)
+
+_TORCH_TO_QMM = {torch.bfloat16: DTYPE_BF16, torch.float16: DTYPE_F16, torch.float32: DTYPE_F32,
+                 torch.int32: DTYPE_I32}
+
+_lib = None
+
+
+class QmmError(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise QmmError(f"{LIB_PATH} is not built; run `python {_PKG / 'build.py'}` (there is no fallback path)")
+        L = ctypes.CDLL(str(LIB_PATH), mode=ctypes.RTLD_GLOBAL)
+        c = ctypes
+        L.qmm_last_error.restype = c.c_char_p
+        L.qmm_version.restype = c.c_int
+        L.qmm_device_status.argtypes = [c.c_int]
+        L.qmm_dynamic_quant.argtypes = [c.c_void_p, c.c_int, c.c_int64, c.c_int64, c.c_int64, c.c_void_p, c.c_int64,
+                                        c.c_void_p, c.c_void_p]
+        L.qmm_quant_matmul_workspace_size.argtypes = [c.c_int64, c.c_int64, c.c_int64, c.c_int,
+                                                      c.POINTER(c.c_size_t)]
+        L.qmm_quant_matmul.argtypes = [c.c_void_p, c.c_int64, c.c_void_p, c.c_int64, c.c_int64, c.c_void_p, c.c_int64,
+                                       c.c_void_p, c.c_void_p, c.c_int, c.c_void_p, c.c_int, c.c_int64, c.c_int64,
+                                       c.c_int64, c.c_int64, c.c_int, c.c_void_p, c.c_size_t, c.c_void_p]
+        L.qmm_weight_quant_batchmatmul.argtypes = [c.c_void_p, c.c_int, c.c_int64, c.c_void_p, c.c_int64, c.c_void_p,
+                                                   c.c_void_p, c.c_int64, c.c_void_p, c.c_void_p, c.c_int64,
+                                                   c.c_int64, c.c_int64, c.c_int64, c.c_void_p]
+        L.qmm_comm_unique_id.argtypes = [c.c_void_p]
+        L.qmm_comm_init_rank.argtypes = [c.c_char_p, c.c_void_p, c.c_int, c.c_int]
+        L.qmm_comm_register.argtypes = [c.c_char_p, c.c_void_p, c.c_int, c.c_int]
+        L.qmm_comm_info.argtypes = [c.c_char_p, c.POINTER(c.c_int), c.POINTER(c.c_int)]
+        L.qmm_comm_destroy.argtypes = [c.c_char_p]
+        L.qmm_mm_all_reduce.argtypes = [c.c_void_p, c.c_int64, c.c_void_p, c.c_int64, c.c_int64, c.c_void_p,
+                                        c.c_int64, c.c_void_p, c.c_void_p, c.c_int, c.c_void_p, c.c_int, c.c_int64,
+                                        c.c_int64, c.c_int64, c.c_int64, c.c_char_p, c.c_char_p, c.c_int64,
+                                        c.c_void_p, c.c_size_t, c.c_void_p]
+        for name in ("qmm_dynamic_quant", "qmm_quant_matmul_workspace_size", "qmm_quant_matmul",
+                     "qmm_weight_quant_batchmatmul", "qmm_comm_unique_id", "qmm_comm_init_rank",
+                     "qmm_comm_register", "qmm_comm_info", "qmm_comm_destroy", "qmm_mm_all_reduce",
+                     "qmm_device_status"):
+            getattr(L, name).restype = c.c_int
+        _lib = L
+    return _lib
+
+
+def check(rc: int, what: str) -> None:
+    if rc != QMM_OK:
+        raise QmmError(f"{what} failed with status {rc}: {lib().qmm_last_error().decode()}")
+
+
+def _ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def dtype_code(dt) -> int:
+    return _TORCH_TO_QMM[dt]
+
+
+def device_status(reset: bool = False) -> int:
+    return lib().qmm_device_status(1 if reset else 0)
+
+
+def dynamic_quant(x: torch.Tensor):
+    """x: [..., cols] bf16/f16 CUDA tensor -> (int8 same shape, fp32 x.shape[:-1])."""
+    assert x.is_cuda and x.stride(-1) == 1
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1 and x2.numel() > 0:
+        x2 = x2.contiguous()
+    rows, cols = x2.shape
+    q = torch.empty((rows, cols), dtype=torch.int8, device=x.device)
+    s = torch.empty((rows,), dtype=torch.float32, device=x.device)
+    ld_x = x2.stride(0) if rows > 1 else max(cols, 1)
+    with torch.cuda.device(x.device):
+        check(lib().qmm_dynamic_quant(_ptr(x2), dtype_code(x.dtype), rows, cols, max(ld_x, cols), _ptr(q),
+                                      max(cols, 1), _ptr(s), _stream()), "qmm_dynamic_quant")
+    return q.reshape(x.shape), s.reshape(x.shape[:-1])
+
+
+def quant_matmul_workspace_size(M: int, N: int, K: int, algo: int = ALGO_AUTO) -> int:
+    n = ctypes.c_size_t(0)
+    check(lib().qmm_quant_matmul_workspace_size(M, N, K, algo, ctypes.byref(n)), "qmm_quant_matmul_workspace_size")
+    return int(n.value)
+
+
+_workspaces = {}
+
+
+def get_workspace(device, nbytes: int) -> torch.Tensor | None:
+    """Zero-initialised scratch, cached per (device, stream); grown by reallocation."""
+    if nbytes == 0:
+        return None
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def quant_matmul(x1, x2, scale, pertoken_scale=None, bias=None, output_dtype=torch.bfloat16, algo=ALGO_AUTO,
+                 out=None):
+    """x1 int8 [M,K]; x2 int8 [K,N] (row-major or a transposed view); see qmm_quant_matmul."""
+    assert x1.is_cuda and x1.dtype == torch.int8 and x2.dtype == torch.int8
+    M, K = x1.shape
+    K2, N = x2.shape
+    assert K == K2
+    if x1.stride(1) != 1 and K > 1:
+        x1 = x1.contiguous()
+    if x2.stride(0) != 1 and x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    sk, sn = x2.stride(0), x2.stride(1)
+    if N == 1 and sk != 1:
+        sn = 1
+    if K == 1 and sn != 1:
+        sk = 1
+    if out is None:
+        out = torch.empty((M, N), dtype=output_dtype, device=x1.device)
+    ws_bytes = quant_matmul_workspace_size(M, N, K, algo)
+    ws = get_workspace(x1.device, ws_bytes)
+    with torch.cuda.device(x1.device):
+        check(lib().qmm_quant_matmul(
+            _ptr(x1), max(x1.stride(0), K, 1) if M > 1 else max(K, 1), _ptr(x2), sk, sn,
+            _ptr(scale), 0 if scale is None else scale.numel(), _ptr(pertoken_scale), _ptr(bias),
+            DTYPE_NONE if bias is None else dtype_code(bias.dtype), _ptr(out), dtype_code(output_dtype),
+            max(out.stride(0), N) if M > 1 else max(N, 1), M, N, K, algo, _ptr(ws), ws_bytes, _stream()),
+            "qmm_quant_matmul")
+    return out
+
+
+def weight_quant_batchmatmul(x, weight, antiquant_scale, antiquant_offset=None, bias=None, group_size=0):
+    """x [M,K] bf16/f16; weight int32 [K, N/8]; scale/offset [K/group, N]."""
+    assert x.is_cuda and weight.dtype == torch.int32
+    M, K = x.shape
+    N = weight.shape[1] * 8
+    group = group_size if group_size > 0 else K
+    x = x.contiguous()
+    weight = weight.contiguous()
+    out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib().qmm_weight_quant_batchmatmul(
+            _ptr(x), dtype_code(x.dtype), K, _ptr(weight), weight.shape[1], _ptr(antiquant_scale.contiguous()),
+            _ptr(None if antiquant_offset is None else antiquant_offset.contiguous()), group,
+            _ptr(None if bias is None else bias.contiguous()), _ptr(out), N, M, N, K, _stream()),
+            "qmm_weight_quant_batchmatmul")
+    return out

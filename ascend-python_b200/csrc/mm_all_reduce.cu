@@ -1,0 +1,314 @@
+// Communicator registry and the row-parallel W8A8 matmul + allreduce
+// (npu_mm_all_reduce_base).
+//
+// The reference hands its fused matmul+collective kernels a communicator NAME
+// (op_plugin/ops/base_ops/opapi/MatmulReduceScatterBaseKernelNpuOpApi.cpp:35-40);
+// the device library resolves it.  Here a name resolves to an NCCL communicator
+// plus one communication stream and a few events.  NCCL is bound at run time
+// with dlopen/dlsym, the way the reference binds its device library
+// (op_plugin/utils/op_api_common.h:80-123), so that the process uses the one
+// libnccl its framework already loaded.
+//
+// Overlap: M is cut into chunks; chunk c's matmul runs on the caller's stream,
+// an event hands the finished rows to the communication stream, whose
+// in-place ncclAllReduce of chunk c runs while chunk c+1 is being multiplied.
+// The matmul leaves a few SMs free while a collective may be in flight.
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <map>
+#include <mutex>
+#include <vector>
+
+#include "qmm_common.cuh"
+#include "w8a8_epilogue.cuh"
+
+namespace qmm {
+
+int quant_matmul_dispatch(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
+                          const EpilogueParams &ep, int out_dtype, int64_t K, int algo, void *workspace,
+                          size_t workspace_bytes, cudaStream_t stream);
+int validate_quant_matmul(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
+                          const float *scale, int64_t scale_len, const void *bias, int bias_dtype, void *out,
+                          int out_dtype, int64_t ld_out, int64_t M, int64_t N, int64_t K);
+void set_sm_reserve(int sms);
+
+namespace {
+
+struct NcclApi {
+    void *handle = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
+    ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t,
+                              cudaStream_t) = nullptr;
+    ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t *) = nullptr;
+    const char *(*GetErrorString)(ncclResult_t) = nullptr;
+    std::string error;
+};
+
+NcclApi &nccl() {
+    static NcclApi api;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        std::vector<std::string> names;
+        if (const char *env = getenv("QMM_NCCL_LIB")) names.emplace_back(env);
+        names.emplace_back("libnccl.so.2");
+        names.emplace_back("libnccl.so");
+        for (const auto &n : names) {
+            api.handle = dlopen(n.c_str(), RTLD_NOW | RTLD_GLOBAL);
+            if (api.handle) break;
+        }
+        if (!api.handle) {
+            api.error = "cannot dlopen libnccl.so.2 (set QMM_NCCL_LIB to its path)";
+            return;
+        }
+        auto sym = [&](const char *name) -> void * {
+            void *p = dlsym(api.handle, name);
+            if (!p && api.error.empty()) api.error = std::string("libnccl lacks symbol ") + name;
+            return p;
+        };
+        api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(sym("ncclGetUniqueId"));
+        api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(sym("ncclCommInitRank"));
+        api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(sym("ncclCommDestroy"));
+        api.CommAbort = reinterpret_cast<decltype(api.CommAbort)>(sym("ncclCommAbort"));
+        api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(sym("ncclAllReduce"));
+        api.CommGetAsyncError = reinterpret_cast<decltype(api.CommGetAsyncError)>(sym("ncclCommGetAsyncError"));
+        api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(sym("ncclGetErrorString"));
+    });
+    return api;
+}
+
+int nccl_ready() {
+    NcclApi &a = nccl();
+    if (!a.error.empty()) return fail(QMM_ERR_NCCL, a.error);
+    return QMM_OK;
+}
+
+#define QMM_NCCL_OK(expr)                                                                          \
+    do {                                                                                           \
+        ncclResult_t _r = (expr);                                                                  \
+        if (_r != ncclSuccess && _r != ncclInProgress)                                             \
+            return ::qmm::fail(QMM_ERR_NCCL, std::string(#expr) + ": " + nccl().GetErrorString(_r)); \
+    } while (0)
+
+constexpr int kMaxChunks = 16;
+
+struct Comm {
+    ncclComm_t comm = nullptr;
+    int nranks = 0;
+    int rank = 0;
+    int device = 0;
+    bool owned = false;
+    cudaStream_t stream = nullptr;  // communication stream
+    cudaEvent_t chunk_ready[kMaxChunks] = {};
+    cudaEvent_t done = nullptr;
+};
+
+std::mutex g_comm_mutex;
+std::map<std::string, Comm> g_comms;
+
+int create_stream_events(Comm &c) {
+    QMM_CUDA_OK(cudaGetDevice(&c.device));
+    int lo = 0, hi = 0;
+    QMM_CUDA_OK(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    QMM_CUDA_OK(cudaStreamCreateWithPriority(&c.stream, cudaStreamNonBlocking, hi));
+    for (auto &e : c.chunk_ready) QMM_CUDA_OK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    QMM_CUDA_OK(cudaEventCreateWithFlags(&c.done, cudaEventDisableTiming));
+    return QMM_OK;
+}
+
+void release(Comm &c, bool abort) {
+    if (c.stream) cudaStreamSynchronize(c.stream);
+    if (c.owned && c.comm) {
+        if (abort)
+            nccl().CommAbort(c.comm);
+        else
+            nccl().CommDestroy(c.comm);
+    }
+    for (auto &e : c.chunk_ready)
+        if (e) cudaEventDestroy(e);
+    if (c.done) cudaEventDestroy(c.done);
+    if (c.stream) cudaStreamDestroy(c.stream);
+    c = Comm();
+}
+
+}  // namespace
+
+}  // namespace qmm
+
+extern "C" int qmm_comm_unique_id(void *id_out) {
+    using namespace qmm;
+    static_assert(sizeof(ncclUniqueId) <= QMM_UNIQUE_ID_BYTES, "unique id does not fit");
+    QMM_REQUIRE(id_out != nullptr, "qmm_comm_unique_id: id_out is NULL");
+    int rc = nccl_ready();
+    if (rc != QMM_OK) return rc;
+    ncclUniqueId id;
+    QMM_NCCL_OK(nccl().GetUniqueId(&id));
+    memset(id_out, 0, QMM_UNIQUE_ID_BYTES);
+    memcpy(id_out, &id, sizeof(id));
+    return QMM_OK;
+}
+
+extern "C" int qmm_comm_init_rank(const char *name, const void *id, int nranks, int rank) {
+    using namespace qmm;
+    QMM_REQUIRE(name != nullptr && name[0] != '\0', "qmm_comm_init_rank: empty communicator name");
+    QMM_REQUIRE(id != nullptr, "qmm_comm_init_rank: id is NULL");
+    QMM_REQUIRE(nranks >= 1 && rank >= 0 && rank < nranks, "qmm_comm_init_rank: rank outside [0, nranks)");
+    int rc = nccl_ready();
+    if (rc != QMM_OK) return rc;
+    {
+        std::lock_guard<std::mutex> lock(g_comm_mutex);
+        if (g_comms.count(name)) return fail(QMM_ERR_INVALID_ARGUMENT, std::string("communicator '") + name +
+                                                                           "' is already registered");
+    }
+    Comm c;
+    c.nranks = nranks;
+    c.rank = rank;
+    c.owned = true;
+    ncclUniqueId uid;
+    memcpy(&uid, id, sizeof(uid));
+    QMM_NCCL_OK(nccl().CommInitRank(&c.comm, nranks, uid, rank));
+    rc = create_stream_events(c);
+    if (rc != QMM_OK) {
+        release(c, true);
+        return rc;
+    }
+    std::lock_guard<std::mutex> lock(g_comm_mutex);
+    g_comms[name] = c;
+    return QMM_OK;
+}
+
+extern "C" int qmm_comm_register(const char *name, void *nccl_comm, int nranks, int rank) {
+    using namespace qmm;
+    QMM_REQUIRE(name != nullptr && name[0] != '\0', "qmm_comm_register: empty communicator name");
+    QMM_REQUIRE(nccl_comm != nullptr, "qmm_comm_register: communicator is NULL");
+    QMM_REQUIRE(nranks >= 1 && rank >= 0 && rank < nranks, "qmm_comm_register: rank outside [0, nranks)");
+    int rc = nccl_ready();
+    if (rc != QMM_OK) return rc;
+    {
+        std::lock_guard<std::mutex> lock(g_comm_mutex);
+        if (g_comms.count(name)) return fail(QMM_ERR_INVALID_ARGUMENT, std::string("communicator '") + name +
+                                                                           "' is already registered");
+    }
+    Comm c;
+    c.comm = static_cast<ncclComm_t>(nccl_comm);
+    c.nranks = nranks;
+    c.rank = rank;
+    c.owned = false;
+    rc = create_stream_events(c);
+    if (rc != QMM_OK) {
+        release(c, true);
+        return rc;
+    }
+    std::lock_guard<std::mutex> lock(g_comm_mutex);
+    g_comms[name] = c;
+    return QMM_OK;
+}
+
+extern "C" int qmm_comm_info(const char *name, int *nranks, int *rank) {
+    using namespace qmm;
+    QMM_REQUIRE(name != nullptr, "qmm_comm_info: name is NULL");
+    std::lock_guard<std::mutex> lock(g_comm_mutex);
+    auto it = g_comms.find(name);
+    if (it == g_comms.end())
+        return fail(QMM_ERR_NOT_FOUND, std::string("communicator '") + name + "' is not registered");
+    if (nranks) *nranks = it->second.nranks;
+    if (rank) *rank = it->second.rank;
+    return QMM_OK;
+}
+
+extern "C" int qmm_comm_destroy(const char *name) {
+    using namespace qmm;
+    QMM_REQUIRE(name != nullptr, "qmm_comm_destroy: name is NULL");
+    Comm c;
+    {
+        std::lock_guard<std::mutex> lock(g_comm_mutex);
+        auto it = g_comms.find(name);
+        if (it == g_comms.end())
+            return fail(QMM_ERR_NOT_FOUND, std::string("communicator '") + name + "' is not registered");
+        c = it->second;
+        g_comms.erase(it);
+    }
+    release(c, false);
+    return QMM_OK;
+}
+
+extern "C" int qmm_mm_all_reduce(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_stride_k,
+                                 int64_t x2_stride_n, const float *scale, int64_t scale_len,
+                                 const float *pertoken_scale, const void *bias, int bias_dtype, void *out,
+                                 int out_dtype, int64_t ld_out, int64_t M, int64_t N, int64_t K, const char *hcom,
+                                 const char *reduce_op, int64_t comm_turn, void *workspace, size_t workspace_bytes,
+                                 void *stream) {
+    using namespace qmm;
+    QMM_REQUIRE(hcom != nullptr && hcom[0] != '\0', "qmm_mm_all_reduce: empty communicator name");
+    QMM_REQUIRE(reduce_op != nullptr && std::string(reduce_op) == "sum",
+                std::string("qmm_mm_all_reduce: reduce_op must be 'sum', got '") + (reduce_op ? reduce_op : "") + "'");
+    QMM_REQUIRE(out_dtype == QMM_DTYPE_BF16 || out_dtype == QMM_DTYPE_F16,
+                "qmm_mm_all_reduce: output dtype must be bf16 or f16");
+    QMM_REQUIRE(comm_turn >= 0, "qmm_mm_all_reduce: comm_turn must be non-negative");
+    int rc = validate_quant_matmul(x1, ld_x1, x2, x2_stride_k, x2_stride_n, scale, scale_len, bias, bias_dtype, out,
+                                   out_dtype, ld_out, M, N, K);
+    if (rc != QMM_OK) return rc;
+    Comm c;
+    {
+        std::lock_guard<std::mutex> lock(g_comm_mutex);
+        auto it = g_comms.find(hcom);
+        if (it == g_comms.end())
+            return fail(QMM_ERR_NOT_FOUND, std::string("communicator '") + hcom + "' is not registered");
+        c = it->second;
+    }
+    if (M == 0 || N == 0) return QMM_OK;
+    QMM_REQUIRE(ld_out == N || M == 1, "qmm_mm_all_reduce: out must be contiguous (ld_out == N)");
+    int dev = 0;
+    QMM_CUDA_OK(cudaGetDevice(&dev));
+    QMM_REQUIRE(dev == c.device, "qmm_mm_all_reduce: communicator belongs to another device");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+    // number of M chunks: each at least 512 rows, so that a chunk still fills the machine
+    int chunks = comm_turn > 0 ? static_cast<int>(comm_turn < kMaxChunks ? comm_turn : kMaxChunks)
+                               : (c.nranks == 1 ? 1 : static_cast<int>(M / 1024));
+    if (chunks < 1) chunks = 1;
+    if (chunks > kMaxChunks) chunks = kMaxChunks;
+    int64_t rows_per = (M + chunks - 1) / chunks;
+    rows_per = (rows_per + 127) / 128 * 128;
+    const size_t elt = 2;
+    const ncclDataType_t dt = out_dtype == QMM_DTYPE_BF16 ? ncclBfloat16 : ncclFloat16;
+
+    int ci = 0;
+    for (int64_t m0 = 0; m0 < M; m0 += rows_per, ++ci) {
+        const int64_t rows = (M - m0) < rows_per ? (M - m0) : rows_per;
+        EpilogueParams ep;
+        ep.scale = scale;
+        ep.pertoken_scale = pertoken_scale ? pertoken_scale + m0 : nullptr;
+        ep.bias = (c.rank == 0) ? bias : nullptr;  // bias enters the sum once
+        ep.bias_dtype = ep.bias ? bias_dtype : QMM_DTYPE_NONE;
+        ep.scale_is_scalar = (scale_len == 1 && N != 1) ? 1 : 0;
+        ep.out = static_cast<uint8_t *>(out) + static_cast<size_t>(m0) * ld_out * elt;
+        ep.ld_out = ld_out;
+        ep.M = rows;
+        ep.N = N;
+        // leave SMs to a collective that may be running beside this chunk
+        set_sm_reserve((c.nranks > 1 && ci > 0) ? 16 : 0);
+        rc = quant_matmul_dispatch(x1 + m0 * ld_x1, ld_x1, x2, x2_stride_k, x2_stride_n, ep, out_dtype, K,
+                                   K == 0 ? QMM_ALGO_SIMT : QMM_ALGO_AUTO, workspace, workspace_bytes, s);
+        set_sm_reserve(0);
+        if (rc != QMM_OK) return rc;
+        if (c.nranks > 1) {
+            QMM_CUDA_OK(cudaEventRecord(c.chunk_ready[ci], s));
+            QMM_CUDA_OK(cudaStreamWaitEvent(c.stream, c.chunk_ready[ci], 0));
+            QMM_NCCL_OK(nccl().AllReduce(ep.out, ep.out, static_cast<size_t>(rows) * N, dt, ncclSum, c.comm,
+                                         c.stream));
+        }
+    }
+    if (c.nranks > 1) {
+        QMM_CUDA_OK(cudaEventRecord(c.done, c.stream));
+        QMM_CUDA_OK(cudaStreamWaitEvent(s, c.done, 0));
+        ncclResult_t async = ncclSuccess;
+        QMM_NCCL_OK(nccl().CommGetAsyncError(c.comm, &async));
+        if (async != ncclSuccess && async != ncclInProgress)
+            return fail(QMM_ERR_NCCL, std::string("NCCL asynchronous error: ") + nccl().GetErrorString(async));
+    }
+    return QMM_OK;
+}

@@ -1,0 +1,453 @@
+// W8A8 matmul with fused dequantization (npu_quant_matmul) for sm_100a.
+//
+// Three kernels:
+//  * w8a8_tile_kernel   — prefill shapes.  Persistent CTAs, one 128x256 output
+//    tile at a time: TMA -> 4-stage shared-memory ring -> tcgen05.mma kind::i8
+//    (128x256x32 per instruction) -> int32 accumulator in TMEM (two buffers, so
+//    the epilogue of tile i overlaps the main loop of tile i+1) -> fused
+//    dequantization epilogue straight from TMEM to global memory.
+//    Warp roles: warp 0 TMA producer, warp 1 MMA issuer + TMEM owner,
+//    warps 2-5 epilogue (each owns the 32 TMEM lanes of its warp_id % 4).
+//  * w8a8_streamk_kernel — decode shapes (M <= 128), weight-bandwidth bound.
+//    (see below)
+//  * w8a8_simt_kernel   — dp4a kernel for operands whose addresses or strides
+//    do not meet the 16-byte rules of TMA.
+//
+// x2 is taken as stored: a row-major [K,N] weight is the MMA's MN-major B
+// operand, the transposed view of a row-major [N,K] weight is its K-major B
+// operand; no repacking pass.
+#include "qmm_common.cuh"
+#include "w8a8_epilogue.cuh"
+
+namespace qmm {
+
+// SMs the persistent tile kernel leaves idle (set around launches that overlap a collective).
+static thread_local int g_sm_reserve = 0;
+void set_sm_reserve(int sms) { g_sm_reserve = sms < 0 ? 0 : sms; }
+
+namespace {
+
+// ---------------------------------------------------------------------------
+// Tile kernel
+// ---------------------------------------------------------------------------
+constexpr int kBM = 128;
+constexpr int kBN = 256;
+constexpr int kBK = 128;  // int8 elements = bytes: one 128-byte swizzle row
+constexpr int kStages = 4;
+constexpr int kAStageBytes = kBM * kBK;
+constexpr int kBStageBytes = kBN * kBK;
+constexpr int kStageBytes = kAStageBytes + kBStageBytes;
+constexpr int kTileThreads = 192;
+constexpr int kGroupM = 16;  // m-tiles per rasterization group
+constexpr uint32_t kTmemCols = 512;
+
+struct TileSmemTail {
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+constexpr size_t kTileSmemBytes = 1024 /*alignment slack*/ + kStages * kStageBytes + sizeof(TileSmemTail);
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int &m_blk, int &n_blk) {
+    const int per_group = kGroupM * tiles_n;
+    const int g = tile / per_group;
+    const int first_m = g * kGroupM;
+    const int rows = min(kGroupM, tiles_m - first_m);
+    const int r = tile - g * per_group;
+    m_blk = first_m + r % rows;
+    n_blk = r / rows;
+}
+
+template <typename OutT, bool B_MN_MAJOR>
+__global__ void __launch_bounds__(kTileThreads, 1)
+w8a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 EpilogueParams ep, int K, uint32_t *status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+    TileSmemTail *tail = reinterpret_cast<TileSmemTail *>(smem_aligned + kStages * kStageBytes);
+    volatile uint32_t *abort_flag = &tail->abort_flag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int tiles_m = static_cast<int>((ep.M + kBM - 1) / kBM);
+    const int tiles_n = static_cast<int>((ep.N + kBN - 1) / kBN);
+    const int num_tiles = tiles_m * tiles_n;
+    const int num_kb = (K + kBK - 1) / kBK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(smem_u32(&tail->full[s]), 1);
+            mbar_init(smem_u32(&tail->empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&tail->tmem_full[b]), 1);
+            mbar_init(smem_u32(&tail->tmem_empty[b]), 4);
+        }
+        tail->abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 0 && lane == 0) {
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tail->tmem_base), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tail->tmem_base;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            int m_blk, n_blk;
+            tile_coords(tile, tiles_m, tiles_n, m_blk, n_blk);
+            for (int kb = 0; kb < num_kb; ++kb) {
+                ok = mbar_wait(smem_u32(&tail->empty[stage]), phase ^ 1, abort_flag, 1);
+                if (!ok) break;
+                if (lane == 0) {
+                    const uint32_t full = smem_u32(&tail->full[stage]);
+                    const uint32_t sa = smem_base + stage * kStageBytes;
+                    const uint32_t sb = sa + kAStageBytes;
+                    mbar_expect_tx(full, kStageBytes);
+                    tma_load_2d(sa, &tmap_a, kb * kBK, m_blk * kBM, full);
+                    if (B_MN_MAJOR) {
+                        // two [128 k-rows x 128 n-bytes] boxes side by side
+                        tma_load_2d(sb, &tmap_b, n_blk * kBN, kb * kBK, full);
+                        tma_load_2d(sb + kBStageBytes / 2, &tmap_b, n_blk * kBN + 128, kb * kBK, full);
+                    } else {
+                        // one [256 n-rows x 128 k-bytes] box
+                        tma_load_2d(sb, &tmap_b, kb * kBK, n_blk * kBN, full);
+                    }
+                }
+                __syncwarp();
+                if (++stage == kStages) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        constexpr uint32_t idesc = make_idesc(/*c=s32*/ 2, /*a=s8*/ 1, /*b=s8*/ 1, /*a K-major*/ 0,
+                                              B_MN_MAJOR ? 1u : 0u, kBM, kBN);
+        uint32_t stage = 0, phase = 0;
+        int local = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+            const uint32_t buf = local & 1;
+            const uint32_t buf_phase = (local >> 1) & 1;
+            ok = mbar_wait(smem_u32(&tail->tmem_empty[buf]), buf_phase ^ 1, abort_flag, 2);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + buf * kBN;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                ok = mbar_wait(smem_u32(&tail->full[stage]), phase, abort_flag, 3);
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t sa = smem_base + stage * kStageBytes;
+                    const uint32_t sb = sa + kAStageBytes;
+#pragma unroll
+                    for (int k = 0; k < kBK / 32; ++k) {
+                        // A: K-major, 128-byte swizzle; 8-row groups 1024 bytes apart; 32 bytes per K step
+                        const uint64_t adesc = make_smem_desc_sw128(sa + k * 32, 16, 1024);
+                        uint64_t bdesc;
+                        if (B_MN_MAJOR) {
+                            // B: MN-major; 128 n-bytes per row, 8 k-row groups 1024 bytes apart,
+                            // second 128-column half 16 KiB further; 32 k-rows (4096 bytes) per K step
+                            bdesc = make_smem_desc_sw128(sb + k * 4096, kBStageBytes / 2, 1024);
+                        } else {
+                            bdesc = make_smem_desc_sw128(sb + k * 32, 16, 1024);
+                        }
+                        mma_i8_ss(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    tc_commit(smem_u32(&tail->empty[stage]));
+                }
+                __syncwarp();
+                if (++stage == kStages) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+            }
+            if (ok && lane == 0) tc_commit(smem_u32(&tail->tmem_full[buf]));
+            __syncwarp();
+        }
+    } else {
+        // ---------------- epilogue warps ----------------
+        const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
+        int local = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+            int m_blk, n_blk;
+            tile_coords(tile, tiles_m, tiles_n, m_blk, n_blk);
+            const uint32_t buf = local & 1;
+            const uint32_t buf_phase = (local >> 1) & 1;
+            ok = mbar_wait(smem_u32(&tail->tmem_full[buf]), buf_phase, abort_flag, 4);
+            if (!ok) break;
+            tc_fence_after();
+            const int64_t m = static_cast<int64_t>(m_blk) * kBM + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBN;
+#pragma unroll 1
+            for (int c = 0; c < kBN / 32; ++c) {
+                uint32_t acc[32];
+                tmem_ld_32x32(taddr + c * 32, acc);
+                tmem_ld_wait();
+                epilogue_row_segment<OutT, 32>(ep, m, static_cast<int64_t>(n_blk) * kBN + c * 32, acc);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&tail->tmem_empty[buf]));
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && tail->abort_flag != 0 && status != nullptr) atomicMax(status, tail->abort_flag);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// SIMT kernel (any stride / alignment): 64x64 tile, 256 threads, 4x4 per thread,
+// int8 operands staged in shared memory with K contiguous, dp4a inner product.
+// ---------------------------------------------------------------------------
+constexpr int kSimtTile = 64;
+constexpr int kSimtK = 64;
+
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+w8a8_simt_kernel(const int8_t *__restrict__ x1, int64_t ld_x1, const int8_t *__restrict__ x2, int64_t x2_sk,
+                 int64_t x2_sn, EpilogueParams ep, int64_t K) {
+    __shared__ int32_t As[kSimtTile][kSimtK / 4 + 1];
+    __shared__ int32_t Bs[kSimtTile][kSimtK / 4 + 1];
+    int8_t *As8 = reinterpret_cast<int8_t *>(&As[0][0]);
+    int8_t *Bs8 = reinterpret_cast<int8_t *>(&Bs[0][0]);
+    constexpr int kRowBytes = (kSimtK / 4 + 1) * 4;
+
+    const int64_t m0 = static_cast<int64_t>(blockIdx.y) * kSimtTile;
+    const int64_t n0 = static_cast<int64_t>(blockIdx.x) * kSimtTile;
+    const int tx = threadIdx.x & 15;  // n direction
+    const int ty = threadIdx.x >> 4;  // m direction
+    int32_t acc[4][4] = {};
+
+    for (int64_t k0 = 0; k0 < K; k0 += kSimtK) {
+        for (int i = threadIdx.x; i < kSimtTile * kSimtK; i += 256) {
+            const int r = i / kSimtK, c = i % kSimtK;  // A: r = m, c = k (k contiguous in memory)
+            const int64_t m = m0 + r, k = k0 + c;
+            As8[r * kRowBytes + c] = (m < ep.M && k < K) ? x1[m * ld_x1 + k] : int8_t(0);
+        }
+        if (x2_sn == 1) {
+            for (int i = threadIdx.x; i < kSimtTile * kSimtK; i += 256) {
+                const int c = i / kSimtTile, r = i % kSimtTile;  // r = n (contiguous in memory), c = k
+                const int64_t n = n0 + r, k = k0 + c;
+                Bs8[r * kRowBytes + c] = (n < ep.N && k < K) ? x2[k * x2_sk + n] : int8_t(0);
+            }
+        } else {
+            for (int i = threadIdx.x; i < kSimtTile * kSimtK; i += 256) {
+                const int r = i / kSimtK, c = i % kSimtK;  // r = n, c = k (k contiguous in memory)
+                const int64_t n = n0 + r, k = k0 + c;
+                Bs8[r * kRowBytes + c] = (n < ep.N && k < K) ? x2[k * x2_sk + n * x2_sn] : int8_t(0);
+            }
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int kk = 0; kk < kSimtK / 4; ++kk) {
+            int32_t a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[ty * 4 + i][kk];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = Bs[tx * 4 + j][kk];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = __dp4a(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) epilogue_one<OutT>(ep, m0 + ty * 4 + i, n0 + tx * 4 + j, acc[i][j]);
+}
+
+// ---------------------------------------------------------------------------
+// Host launchers
+// ---------------------------------------------------------------------------
+template <typename OutT>
+int launch_tile(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
+                const EpilogueParams &ep, int64_t K, cudaStream_t stream) {
+    CUtensorMap ta, tb;
+    int rc = make_tmap_2d(&ta, x1, 1, static_cast<uint64_t>(K), static_cast<uint64_t>(ep.M),
+                          static_cast<uint64_t>(ld_x1), kBK, kBM, true);
+    if (rc != QMM_OK) return rc;
+    const bool mn_major = (x2_sn == 1);
+    if (mn_major) {
+        rc = make_tmap_2d(&tb, x2, 1, static_cast<uint64_t>(ep.N), static_cast<uint64_t>(K),
+                          static_cast<uint64_t>(x2_sk), 128, kBK, true);
+    } else {
+        rc = make_tmap_2d(&tb, x2, 1, static_cast<uint64_t>(K), static_cast<uint64_t>(ep.N),
+                          static_cast<uint64_t>(x2_sn), kBK, kBN, true);
+    }
+    if (rc != QMM_OK) return rc;
+    const int tiles = static_cast<int>(((ep.M + kBM - 1) / kBM) * ((ep.N + kBN - 1) / kBN));
+    int ctas = sm_count() - g_sm_reserve;
+    if (ctas < 1) ctas = 1;
+    const int grid = tiles < ctas ? tiles : ctas;
+    uint32_t *status = device_status_word();
+    auto kern = mn_major ? w8a8_tile_kernel<OutT, true> : w8a8_tile_kernel<OutT, false>;
+    QMM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(kTileSmemBytes)));
+    kern<<<grid, kTileThreads, kTileSmemBytes, stream>>>(ta, tb, ep, static_cast<int>(K), status);
+    QMM_CUDA_OK(cudaGetLastError());
+    return QMM_OK;
+}
+
+template <typename OutT>
+int launch_simt(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
+                const EpilogueParams &ep, int64_t K, cudaStream_t stream) {
+    dim3 grid(static_cast<unsigned>((ep.N + kSimtTile - 1) / kSimtTile),
+              static_cast<unsigned>((ep.M + kSimtTile - 1) / kSimtTile));
+    if (grid.y > 65535) return fail(QMM_ERR_UNSUPPORTED, "qmm_quant_matmul: M too large for the SIMT kernel");
+    w8a8_simt_kernel<OutT><<<grid, 256, 0, stream>>>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K);
+    QMM_CUDA_OK(cudaGetLastError());
+    return QMM_OK;
+}
+
+bool tma_compatible(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn) {
+    if ((reinterpret_cast<uintptr_t>(x1) & 15) || (ld_x1 & 15)) return false;
+    if (reinterpret_cast<uintptr_t>(x2) & 15) return false;
+    if (x2_sn == 1) return (x2_sk & 15) == 0;
+    if (x2_sk == 1) return (x2_sn & 15) == 0;
+    return false;
+}
+
+}  // namespace
+
+// Implemented in w8a8_streamk.cu
+int launch_streamk(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
+                   const EpilogueParams &ep, int out_dtype, int64_t K, void *workspace, size_t workspace_bytes,
+                   cudaStream_t stream);
+size_t streamk_workspace_bytes(int64_t M, int64_t N, int64_t K);
+bool streamk_supported(int64_t M, int64_t N, int64_t K, int64_t x2_sn);
+
+int quant_matmul_dispatch(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
+                          const EpilogueParams &ep, int out_dtype, int64_t K, int algo, void *workspace,
+                          size_t workspace_bytes, cudaStream_t stream) {
+    const bool tma_ok = tma_compatible(x1, ld_x1, x2, x2_sk, x2_sn) && K < (1ll << 31) && ep.M < (1ll << 31) &&
+                        ep.N < (1ll << 31);
+    if (algo == QMM_ALGO_AUTO) {
+        if (!tma_ok)
+            algo = QMM_ALGO_SIMT;
+        else if (streamk_supported(ep.M, ep.N, K, x2_sn) && workspace != nullptr &&
+                 workspace_bytes >= streamk_workspace_bytes(ep.M, ep.N, K))
+            algo = QMM_ALGO_TCGEN05_STREAMK;
+        else
+            algo = QMM_ALGO_TCGEN05_TILE;
+    }
+    if ((algo == QMM_ALGO_TCGEN05_TILE || algo == QMM_ALGO_TCGEN05_STREAMK) && !tma_ok)
+        return fail(QMM_ERR_UNSUPPORTED,
+                    "qmm_quant_matmul: tcgen05 kernels need 16-byte aligned operands and row pitches");
+    switch (algo) {
+        case QMM_ALGO_TCGEN05_TILE:
+            switch (out_dtype) {
+                case QMM_DTYPE_BF16:
+                    return launch_tile<__nv_bfloat16>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, stream);
+                case QMM_DTYPE_F16:
+                    return launch_tile<__half>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, stream);
+                default:
+                    return launch_tile<int32_t>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, stream);
+            }
+        case QMM_ALGO_TCGEN05_STREAMK:
+            return launch_streamk(x1, ld_x1, x2, x2_sk, x2_sn, ep, out_dtype, K, workspace, workspace_bytes, stream);
+        case QMM_ALGO_SIMT:
+            switch (out_dtype) {
+                case QMM_DTYPE_BF16:
+                    return launch_simt<__nv_bfloat16>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, stream);
+                case QMM_DTYPE_F16:
+                    return launch_simt<__half>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, stream);
+                default:
+                    return launch_simt<int32_t>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, stream);
+            }
+        default:
+            return fail(QMM_ERR_INVALID_ARGUMENT, "qmm_quant_matmul: unknown algo");
+    }
+}
+
+int validate_quant_matmul(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
+                          const float *scale, int64_t scale_len, const void *bias, int bias_dtype, void *out,
+                          int out_dtype, int64_t ld_out, int64_t M, int64_t N, int64_t K) {
+    QMM_REQUIRE(M >= 0 && N >= 0 && K >= 0, "qmm_quant_matmul: negative dimension");
+    QMM_REQUIRE(out_dtype == QMM_DTYPE_BF16 || out_dtype == QMM_DTYPE_F16 || out_dtype == QMM_DTYPE_I32,
+                "qmm_quant_matmul: output dtype must be bf16, f16 or int32");
+    if (M == 0 || N == 0) return QMM_OK;
+    QMM_REQUIRE(out != nullptr, "qmm_quant_matmul: out is NULL");
+    QMM_REQUIRE(ld_out >= N, "qmm_quant_matmul: ld_out smaller than N");
+    if (K > 0) {
+        QMM_REQUIRE(x1 != nullptr && x2 != nullptr, "qmm_quant_matmul: NULL operand");
+        QMM_REQUIRE(ld_x1 >= K, "qmm_quant_matmul: ld_x1 smaller than K");
+        QMM_REQUIRE(x2_sk == 1 || x2_sn == 1, "qmm_quant_matmul: x2 must have a unit stride along K or N");
+        QMM_REQUIRE((x2_sn == 1 && (x2_sk >= N || K == 1)) || (x2_sk == 1 && (x2_sn >= K || N == 1)),
+                    "qmm_quant_matmul: x2 strides overlap");
+    }
+    if (out_dtype != QMM_DTYPE_I32) {
+        QMM_REQUIRE(scale != nullptr, "qmm_quant_matmul: scale is NULL");
+        QMM_REQUIRE(scale_len == N || scale_len == 1, "qmm_quant_matmul: scale must have N elements or one");
+        QMM_REQUIRE(bias == nullptr || bias_dtype == QMM_DTYPE_BF16 || bias_dtype == QMM_DTYPE_F16 ||
+                        bias_dtype == QMM_DTYPE_F32,
+                    "qmm_quant_matmul: bias must be bf16, f16 or f32 for a floating-point output");
+    } else {
+        QMM_REQUIRE(bias == nullptr || bias_dtype == QMM_DTYPE_I32,
+                    "qmm_quant_matmul: bias must be int32 for an int32 output");
+    }
+    return QMM_OK;
+}
+
+}  // namespace qmm
+
+extern "C" int qmm_quant_matmul_workspace_size(int64_t M, int64_t N, int64_t K, int algo, size_t *bytes) {
+    using namespace qmm;
+    QMM_REQUIRE(bytes != nullptr, "qmm_quant_matmul_workspace_size: bytes is NULL");
+    QMM_REQUIRE(M >= 0 && N >= 0 && K >= 0, "qmm_quant_matmul_workspace_size: negative dimension");
+    *bytes = 0;
+    if ((algo == QMM_ALGO_AUTO || algo == QMM_ALGO_TCGEN05_STREAMK) && streamk_supported(M, N, K, 1))
+        *bytes = streamk_workspace_bytes(M, N, K);
+    return QMM_OK;
+}
+
+extern "C" int qmm_quant_matmul(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_stride_k,
+                                int64_t x2_stride_n, const float *scale, int64_t scale_len,
+                                const float *pertoken_scale, const void *bias, int bias_dtype, void *out,
+                                int out_dtype, int64_t ld_out, int64_t M, int64_t N, int64_t K, int algo,
+                                void *workspace, size_t workspace_bytes, void *stream) {
+    using namespace qmm;
+    int rc = validate_quant_matmul(x1, ld_x1, x2, x2_stride_k, x2_stride_n, scale, scale_len, bias, bias_dtype, out,
+                                   out_dtype, ld_out, M, N, K);
+    if (rc != QMM_OK) return rc;
+    if (M == 0 || N == 0) return QMM_OK;
+    EpilogueParams ep;
+    ep.scale = scale;
+    ep.pertoken_scale = (out_dtype == QMM_DTYPE_I32) ? nullptr : pertoken_scale;
+    ep.bias = bias;
+    ep.bias_dtype = bias ? bias_dtype : QMM_DTYPE_NONE;
+    ep.scale_is_scalar = (scale_len == 1 && N != 1) ? 1 : 0;
+    ep.out = out;
+    ep.ld_out = ld_out;
+    ep.M = M;
+    ep.N = N;
+    if (K == 0) algo = QMM_ALGO_SIMT;  // empty reduction: epilogue of zeros
+    return quant_matmul_dispatch(x1, ld_x1, x2, x2_stride_k, x2_stride_n, ep, out_dtype, K, algo, workspace,
+                                 workspace_bytes, static_cast<cudaStream_t>(stream));
+}

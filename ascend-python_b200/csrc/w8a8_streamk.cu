@@ -1,0 +1,368 @@
+// W8A8 matmul for decode shapes (M <= 128): weight-bandwidth bound.
+//
+// The weight tile is the MMA's 128-row M operand (rows = output columns n),
+// the activations are its N operand (M padded to a multiple of 16), so no
+// tensor-core lane is wasted on padding beyond 16 tokens and each accumulator
+// lane maps to one output column: stores of a token row are coalesced.
+//
+// The (n-tile, k-block) space is cut into gridDim.x equal contiguous ranges
+// ("stream-K"): every CTA streams the same number of 16 KiB weight tiles
+// whatever N and K are.  A CTA whose range covers a whole K extent finishes
+// the tile itself; otherwise it adds its int32 partial sums into a scratch
+// accumulator with red.global.add (integer addition: the result does not
+// depend on arrival order) and the CTA that completes the tile's k-block count
+// applies the epilogue and re-zeroes the scratch for the next call.
+#include "qmm_common.cuh"
+#include "w8a8_epilogue.cuh"
+
+namespace qmm {
+
+namespace {
+
+constexpr int kSkTileN = 128;  // output columns per tile = MMA M
+constexpr int kSkBK = 128;     // k elements per stage
+constexpr int kSkABytes = kSkTileN * kSkBK;
+constexpr int kSkMaxStages = 8;
+constexpr int kSkThreads = 192;
+constexpr uint32_t kSkTmemCols = 256;  // two accumulators of up to 128 columns
+constexpr size_t kSkSmemBudget = 200 * 1024;
+
+struct SkSmemTail {
+    uint64_t full[kSkMaxStages];
+    uint64_t empty[kSkMaxStages];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+    uint32_t is_last;
+    uint32_t epi_abort;
+};
+
+struct SkParams {
+    EpilogueParams ep;
+    int K;
+    int mpad;         // M rounded up to a multiple of 16
+    int stages;
+    int stage_bytes;  // kSkABytes + mpad * kSkBK
+    int tiles_n;
+    int kblocks;
+    int32_t *ws_acc;      // [tiles_n][mpad][128] int32, zero between calls
+    uint32_t *ws_count;   // [tiles_n], zero between calls
+    uint32_t *status;
+};
+
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+template <typename OutT, bool A_MN_MAJOR>
+__global__ void __launch_bounds__(kSkThreads, 1)
+w8a8_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                    SkParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+    SkSmemTail *tail = reinterpret_cast<SkSmemTail *>(smem_aligned + p.stages * p.stage_bytes);
+    volatile uint32_t *abort_flag = &tail->abort_flag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    // this CTA's contiguous range of (tile, k-block) units
+    const int64_t total = static_cast<int64_t>(p.tiles_n) * p.kblocks;
+    const int64_t u_begin = total * blockIdx.x / gridDim.x;
+    const int64_t u_end = total * (blockIdx.x + 1) / gridDim.x;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(smem_u32(&tail->full[s]), 1);
+            mbar_init(smem_u32(&tail->empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&tail->tmem_full[b]), 1);
+            mbar_init(smem_u32(&tail->tmem_empty[b]), 4);
+        }
+        tail->abort_flag = 0;
+        tail->is_last = 0;
+        tail->epi_abort = 0;
+        mbar_fence_init();
+    }
+    if (warp == 0 && lane == 0) {
+        tma_prefetch_desc(&tmap_w);
+        tma_prefetch_desc(&tmap_x);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tail->tmem_base), kSkTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tail->tmem_base;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        uint32_t stage = 0, phase = 0;
+        for (int64_t u = u_begin; u < u_end; ++u) {
+            const int tile = static_cast<int>(u / p.kblocks);
+            const int kb = static_cast<int>(u - static_cast<int64_t>(tile) * p.kblocks);
+            if (!mbar_wait(smem_u32(&tail->empty[stage]), phase ^ 1, abort_flag, 0x11)) break;
+            if (lane == 0) {
+                const uint32_t full = smem_u32(&tail->full[stage]);
+                const uint32_t sa = smem_base + stage * p.stage_bytes;
+                const uint32_t sb = sa + kSkABytes;
+                mbar_expect_tx(full, static_cast<uint32_t>(p.stage_bytes));
+                if (A_MN_MAJOR)
+                    tma_load_2d(sa, &tmap_w, tile * kSkTileN, kb * kSkBK, full);  // [128 k-rows][128 n-bytes]
+                else
+                    tma_load_2d(sa, &tmap_w, kb * kSkBK, tile * kSkTileN, full);  // [128 n-rows][128 k-bytes]
+                tma_load_2d(sb, &tmap_x, kb * kSkBK, 0, full);                    // [mpad m-rows][128 k-bytes]
+            }
+            __syncwarp();
+            if (++stage == static_cast<uint32_t>(p.stages)) {
+                stage = 0;
+                phase ^= 1;
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        const uint32_t idesc = make_idesc(/*c=s32*/ 2, 1, 1, A_MN_MAJOR ? 1u : 0u, /*b K-major*/ 0, kSkTileN,
+                                          static_cast<uint32_t>(p.mpad));
+        uint32_t stage = 0, phase = 0;
+        int seg = 0;
+        bool ok = true;
+        int64_t u = u_begin;
+        while (u < u_end && ok) {
+            const int tile = static_cast<int>(u / p.kblocks);
+            const int64_t tile_end = static_cast<int64_t>(tile + 1) * p.kblocks;
+            const int64_t seg_end = tile_end < u_end ? tile_end : u_end;
+            const uint32_t buf = seg & 1;
+            const uint32_t buf_phase = (seg >> 1) & 1;
+            ok = mbar_wait(smem_u32(&tail->tmem_empty[buf]), buf_phase ^ 1, abort_flag, 0x12);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + buf * 128;
+            bool first = true;
+            for (; u < seg_end; ++u) {
+                ok = mbar_wait(smem_u32(&tail->full[stage]), phase, abort_flag, 0x13);
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t sa = smem_base + stage * p.stage_bytes;
+                    const uint32_t sb = sa + kSkABytes;
+#pragma unroll
+                    for (int k = 0; k < kSkBK / 32; ++k) {
+                        const uint64_t adesc = A_MN_MAJOR ? make_smem_desc_sw128(sa + k * 4096, 1024, 1024)
+                                                          : make_smem_desc_sw128(sa + k * 32, 16, 1024);
+                        const uint64_t bdesc = make_smem_desc_sw128(sb + k * 32, 16, 1024);
+                        mma_i8_ss(d_tmem, adesc, bdesc, idesc, (first && k == 0) ? 0u : 1u);
+                    }
+                    tc_commit(smem_u32(&tail->empty[stage]));
+                }
+                first = false;
+                __syncwarp();
+                if (++stage == static_cast<uint32_t>(p.stages)) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+            }
+            if (ok && lane == 0) tc_commit(smem_u32(&tail->tmem_full[buf]));
+            __syncwarp();
+            ++seg;
+        }
+    } else {
+        // ---------------- epilogue warps ----------------
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;  // accumulator lane = output column within the tile
+        const bool leader = (threadIdx.x == 64);
+        const EpilogueParams &ep = p.ep;
+        const int M = static_cast<int>(ep.M);
+        int seg = 0;
+        bool ok = true;
+        int64_t u = u_begin;
+        while (u < u_end && ok) {
+            const int tile = static_cast<int>(u / p.kblocks);
+            const int64_t tile_begin = static_cast<int64_t>(tile) * p.kblocks;
+            const int64_t tile_end = tile_begin + p.kblocks;
+            const int64_t seg_end = tile_end < u_end ? tile_end : u_end;
+            const bool whole = (u == tile_begin && seg_end == tile_end);
+            const uint32_t units = static_cast<uint32_t>(seg_end - u);
+            const uint32_t buf = seg & 1;
+            const uint32_t buf_phase = (seg >> 1) & 1;
+            ok = mbar_wait(smem_u32(&tail->tmem_full[buf]), buf_phase, abort_flag, 0x14);
+            // The four epilogue warps meet at named barriers below, so they must
+            // leave the loop together: agree on the outcome of the wait first.
+            if (!ok) *reinterpret_cast<volatile uint32_t *>(&tail->epi_abort) = 1;
+            epi_bar_sync();
+            if (*reinterpret_cast<volatile uint32_t *>(&tail->epi_abort) != 0) break;
+            tc_fence_after();
+
+            const int64_t n = static_cast<int64_t>(tile) * kSkTileN + row;
+            const bool n_ok = n < ep.N;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * 128;
+
+            // per-column constants of the dequantization
+            float sc = 0.0f, bi = 0.0f;
+            int32_t bi32 = 0;
+            const bool has_pt = (ep.pertoken_scale != nullptr);
+            bool has_bias = false;
+            if (n_ok) {
+                if constexpr (sizeof(OutT) == 4) {
+                    has_bias = (ep.bias != nullptr && ep.bias_dtype == QMM_DTYPE_I32);
+                    if (has_bias) bi32 = __ldg(static_cast<const int32_t *>(ep.bias) + n);
+                } else {
+                    has_bias = (ep.bias != nullptr && ep.bias_dtype != QMM_DTYPE_NONE &&
+                                ep.bias_dtype != QMM_DTYPE_I32);
+                    sc = ep.scale_is_scalar ? __ldg(ep.scale) : __ldg(ep.scale + n);
+                    if (has_bias) bi = load_bias_f32(ep, n);
+                }
+            }
+            auto finish = [&](int m, int32_t acc) {
+                OutT *o = static_cast<OutT *>(ep.out) + static_cast<int64_t>(m) * ep.ld_out + n;
+                if constexpr (sizeof(OutT) == 4) {
+                    *reinterpret_cast<int32_t *>(o) = acc + bi32;
+                } else {
+                    const float pt = has_pt ? __ldg(ep.pertoken_scale + m) : 1.0f;
+                    *o = from_float<OutT>(dequant_one(acc, sc, pt, has_pt, bi, has_bias));
+                }
+            };
+
+            int32_t *ws = p.ws_acc + (static_cast<int64_t>(tile) * p.mpad) * kSkTileN + row;
+            for (int c = 0; c < p.mpad; c += 16) {
+                uint32_t acc[16];
+                tmem_ld_32x16(taddr + c, acc);
+                tmem_ld_wait();
+                if (n_ok) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int m = c + j;
+                        if (m < M) {
+                            if (whole)
+                                finish(m, static_cast<int32_t>(acc[j]));
+                            else
+                                atomicAdd(ws + static_cast<int64_t>(m) * kSkTileN, static_cast<int32_t>(acc[j]));
+                        }
+                    }
+                }
+            }
+            // accumulator buffer can be reused by the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&tail->tmem_empty[buf]));
+
+            if (!whole) {
+                // publish the partial sums, then find out whether this CTA completed the tile
+                epi_bar_sync();
+                if (leader) {
+                    __threadfence();
+                    const uint32_t old = atomicAdd(p.ws_count + tile, units);
+                    tail->is_last = (old + units == static_cast<uint32_t>(p.kblocks)) ? 1u : 0u;
+                    __threadfence();
+                }
+                epi_bar_sync();
+                if (tail->is_last) {
+                    if (n_ok) {
+                        for (int m = 0; m < M; ++m) {
+                            int32_t *a = ws + static_cast<int64_t>(m) * kSkTileN;
+                            const int32_t v = __ldcg(a);
+                            __stcg(a, 0);
+                            finish(m, v);
+                        }
+                    }
+                    if (leader) p.ws_count[tile] = 0;
+                }
+                epi_bar_sync();  // is_last is rewritten by the next split segment
+            }
+            u = seg_end;
+            ++seg;
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && tail->abort_flag != 0 && p.status != nullptr) atomicMax(p.status, tail->abort_flag);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kSkTmemCols);
+    }
+}
+
+int mpad_of(int64_t M) { return static_cast<int>((M + 15) / 16 * 16); }
+
+}  // namespace
+
+bool streamk_supported(int64_t M, int64_t N, int64_t K, int64_t x2_sn) {
+    (void)x2_sn;
+    return M >= 1 && M <= 128 && N >= 1 && K >= 1;
+}
+
+size_t streamk_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+    (void)K;
+    const int64_t tiles_n = (N + kSkTileN - 1) / kSkTileN;
+    const size_t acc = static_cast<size_t>(tiles_n) * mpad_of(M) * kSkTileN * sizeof(int32_t);
+    const size_t cnt = (static_cast<size_t>(tiles_n) * sizeof(uint32_t) + 255) / 256 * 256;
+    return acc + cnt;
+}
+
+template <typename OutT>
+static int launch_streamk_t(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
+                            const EpilogueParams &ep, int64_t K, void *workspace, cudaStream_t stream) {
+    SkParams p;
+    p.ep = ep;
+    p.K = static_cast<int>(K);
+    p.mpad = mpad_of(ep.M);
+    p.stage_bytes = kSkABytes + p.mpad * kSkBK;
+    int stages = static_cast<int>((kSkSmemBudget - 1024 - sizeof(SkSmemTail)) / p.stage_bytes);
+    p.stages = stages > kSkMaxStages ? kSkMaxStages : stages;
+    p.tiles_n = static_cast<int>((ep.N + kSkTileN - 1) / kSkTileN);
+    p.kblocks = static_cast<int>((K + kSkBK - 1) / kSkBK);
+    const size_t acc_bytes = static_cast<size_t>(p.tiles_n) * p.mpad * kSkTileN * sizeof(int32_t);
+    p.ws_acc = static_cast<int32_t *>(workspace);
+    p.ws_count = reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(workspace) + acc_bytes);
+    p.status = device_status_word();
+
+    const bool mn_major = (x2_sn == 1);
+    CUtensorMap tw, tx;
+    int rc;
+    if (mn_major)
+        rc = make_tmap_2d(&tw, x2, 1, static_cast<uint64_t>(ep.N), static_cast<uint64_t>(K),
+                          static_cast<uint64_t>(x2_sk), 128, kSkBK, true);
+    else
+        rc = make_tmap_2d(&tw, x2, 1, static_cast<uint64_t>(K), static_cast<uint64_t>(ep.N),
+                          static_cast<uint64_t>(x2_sn), kSkBK, kSkTileN, true);
+    if (rc != QMM_OK) return rc;
+    rc = make_tmap_2d(&tx, x1, 1, static_cast<uint64_t>(K), static_cast<uint64_t>(ep.M),
+                      static_cast<uint64_t>(ld_x1), kSkBK, static_cast<uint32_t>(p.mpad), true);
+    if (rc != QMM_OK) return rc;
+
+    const int64_t total = static_cast<int64_t>(p.tiles_n) * p.kblocks;
+    const int grid = total < sm_count() ? static_cast<int>(total) : sm_count();
+    const size_t smem = 1024 + static_cast<size_t>(p.stages) * p.stage_bytes + sizeof(SkSmemTail);
+    auto kern = mn_major ? w8a8_streamk_kernel<OutT, true> : w8a8_streamk_kernel<OutT, false>;
+    QMM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(kSkSmemBudget)));
+    kern<<<grid, kSkThreads, smem, stream>>>(tw, tx, p);
+    QMM_CUDA_OK(cudaGetLastError());
+    return QMM_OK;
+}
+
+int launch_streamk(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
+                   const EpilogueParams &ep, int out_dtype, int64_t K, void *workspace, size_t workspace_bytes,
+                   cudaStream_t stream) {
+    if (!streamk_supported(ep.M, ep.N, K, x2_sn))
+        return fail(QMM_ERR_UNSUPPORTED, "qmm_quant_matmul: the stream-K kernel handles 1 <= M <= 128 only");
+    if (workspace == nullptr || workspace_bytes < streamk_workspace_bytes(ep.M, ep.N, K))
+        return fail(QMM_ERR_WORKSPACE, "qmm_quant_matmul: workspace missing or smaller than "
+                                       "qmm_quant_matmul_workspace_size reports");
+    if (reinterpret_cast<uintptr_t>(workspace) & 15)
+        return fail(QMM_ERR_WORKSPACE, "qmm_quant_matmul: workspace must be 16-byte aligned");
+    switch (out_dtype) {
+        case QMM_DTYPE_BF16:
+            return launch_streamk_t<__nv_bfloat16>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, workspace, stream);
+        case QMM_DTYPE_F16:
+            return launch_streamk_t<__half>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, workspace, stream);
+        default:
+            return launch_streamk_t<int32_t>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, workspace, stream);
+    }
+}
+
+}  // namespace qmm

@@ -1,0 +1,172 @@
+/*
+ * qmm_b200.h — C ABI of the B200 quantized-matmul library (libqmm_b200.so).
+ *
+ * This is the launch boundary the operator host code binds to.  In the
+ * reference plugin the same role is played by the `aclnn*` symbols that
+ * `EXEC_NPU_CMD` resolves with dlsym and calls in two phases
+ * (op_plugin/utils/op_api_common.h:62, :520-570): a `...GetWorkspaceSize`
+ * query followed by the launch on an explicit stream, `0` meaning success and
+ * any other value being turned into a TORCH_CHECK failure that quotes the
+ * library's last error text (op_api_common.h:546,555).  The functions below
+ * keep that convention: plain pointers and sizes, an explicit stream, an `int`
+ * status, `qmm_last_error()` for the message.  No torch types, no exceptions.
+ *
+ * All device pointers must belong to the device that is current on the calling
+ * thread.  Every launch is asynchronous on `stream` (a `cudaStream_t`, passed
+ * as `void*` so that this header needs no CUDA include).
+ */
+#ifndef QMM_B200_H_
+#define QMM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define QMM_API __attribute__((visibility("default")))
+#else
+#define QMM_API
+#endif
+
+/* Status codes (0 = success, like the aclnn convention). */
+enum {
+    QMM_OK = 0,
+    QMM_ERR_INVALID_ARGUMENT = 1,
+    QMM_ERR_UNSUPPORTED = 2,
+    QMM_ERR_CUDA = 3,
+    QMM_ERR_NCCL = 4,
+    QMM_ERR_NOT_FOUND = 5,
+    QMM_ERR_WORKSPACE = 6,
+    QMM_ERR_DEVICE_TIMEOUT = 7
+};
+
+/* Element types of activations, biases and outputs. */
+enum {
+    QMM_DTYPE_BF16 = 0,
+    QMM_DTYPE_F16 = 1,
+    QMM_DTYPE_F32 = 2,
+    QMM_DTYPE_I32 = 3,
+    QMM_DTYPE_NONE = -1
+};
+
+/* Kernel selection for qmm_quant_matmul (QMM_ALGO_AUTO in production). */
+enum {
+    QMM_ALGO_AUTO = 0,
+    QMM_ALGO_TCGEN05_TILE = 1,   /* 128x256 output tiles, one CTA per tile (prefill) */
+    QMM_ALGO_TCGEN05_STREAMK = 2, /* weights as the MMA's M operand, K split over CTAs (decode) */
+    QMM_ALGO_SIMT = 3            /* dp4a kernel: any alignment, any stride */
+};
+
+/* Text of the last error raised on the calling thread ("" if none). */
+QMM_API const char *qmm_last_error(void);
+
+/* Library version: major*10000 + minor*100 + patch. */
+QMM_API int qmm_version(void);
+
+/*
+ * Status word written by kernels whose bounded device-side waits gave up
+ * (0 = no wait ever timed out on this device).  Reads host-mapped memory: call
+ * after synchronizing the stream.  `reset` != 0 clears it.
+ */
+QMM_API int qmm_device_status(int reset);
+
+/*
+ * Per-token dynamic quantization (torch op `npu_dynamic_quant`; the op is not
+ * in the reference snapshot, its host conventions follow
+ * op_plugin/ops/base_ops/aclops/QuantizePerChannelKernelNpu.cpp:69-92).
+ *   amax[r]  = max_c |x[r,c]|            (fp32)
+ *   scale[r] = amax[r] / 127             (fp32 division)
+ *   q[r,c]   = clamp(rint(x[r,c] / scale[r]), -128, 127), rows with amax==0 -> 0
+ * x: [rows, cols] bf16/f16, row stride ld_x elements; q: int8 row stride ld_q;
+ * scale: [rows] fp32.
+ */
+QMM_API int qmm_dynamic_quant(const void *x, int x_dtype, int64_t rows, int64_t cols, int64_t ld_x,
+                              int8_t *q, int64_t ld_q, float *scale, void *stream);
+
+/*
+ * Bytes of scratch memory qmm_quant_matmul needs for a problem (first phase
+ * of the two-phase call, cf. `aclnnXGetWorkspaceSize`, op_api_common.h:543-546).
+ * May be 0.  The scratch must be zero-filled before its FIRST use only; the
+ * kernels leave it zeroed again.
+ */
+QMM_API int qmm_quant_matmul_workspace_size(int64_t M, int64_t N, int64_t K, int algo, size_t *bytes);
+
+/*
+ * W8A8 matmul with fused dequantization (torch op `npu_quant_matmul`; host
+ * conventions follow op_plugin/ops/base_ops/opapi/MmKernelNpuOpApi.cpp:24-42).
+ *   acc[m,n] = sum_k x1[m,k] * x2[k,n]                       (int32, exact)
+ *   out_dtype == I32 : out = acc (+ bias if bias_dtype == I32)
+ *   else             : out = cast(float(acc) * scale[n] * pertoken_scale[m] + bias[n])
+ * x1: int8 [M,K], row stride ld_x1.  x2: int8 [K,N] addressed as
+ * x2[k*x2_stride_k + n*x2_stride_n]; one of the two strides must be 1
+ * (row-major [K,N], or the transposed view of a row-major [N,K]).
+ * scale: fp32, scale_len is N or 1.  pertoken_scale: fp32 [M] or NULL.
+ * bias: [N] of bias_dtype, or NULL with QMM_DTYPE_NONE.
+ * out: [M,N] of out_dtype (BF16, F16 or I32), row stride ld_out.
+ * workspace: at least the queried size (may be NULL when that is 0).
+ */
+QMM_API int qmm_quant_matmul(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_stride_k,
+                             int64_t x2_stride_n, const float *scale, int64_t scale_len,
+                             const float *pertoken_scale, const void *bias, int bias_dtype, void *out,
+                             int out_dtype, int64_t ld_out, int64_t M, int64_t N, int64_t K, int algo,
+                             void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * W4A16 matmul (torch op `npu_weight_quant_batchmatmul`; host conventions as
+ * above plus the bias handling of
+ * op_plugin/ops/base_ops/aclops/LinearKernelNpu.cpp:29-45).
+ *   W[k,n]  = (w4[k,n] + offset[k/group, n]) * scale[k/group, n]
+ *   out     = cast(x @ W + bias)
+ * x: [M,K] bf16/f16 (x_dtype), row stride ld_x.  weight: int32 [K, N/8], row
+ * stride ld_w words; nibble j of word i holds column 8*i+j as a two's
+ * complement 4-bit integer.  antiquant_scale / antiquant_offset:
+ * [K/group, N] of x_dtype (offset may be NULL = 0).  group must divide K and
+ * be a multiple of 32; group == K gives per-channel quantization.
+ * out: [M,N] of x_dtype, row stride ld_out.
+ */
+QMM_API int qmm_weight_quant_batchmatmul(const void *x, int x_dtype, int64_t ld_x, const int32_t *weight,
+                                         int64_t ld_w, const void *antiquant_scale,
+                                         const void *antiquant_offset, int64_t group, const void *bias,
+                                         void *out, int64_t ld_out, int64_t M, int64_t N, int64_t K,
+                                         void *stream);
+
+/*
+ * Communicator registry.  The reference passes a communicator NAME into its
+ * fused matmul+collective kernels (`hcom`,
+ * op_plugin/ops/base_ops/opapi/MatmulReduceScatterBaseKernelNpuOpApi.cpp:35-40)
+ * which the device library resolves.  Here the name resolves to an NCCL
+ * communicator created by qmm_comm_init_rank (all ranks call it with the id
+ * rank 0 obtained from qmm_comm_unique_id) or adopted with qmm_comm_register.
+ */
+#define QMM_UNIQUE_ID_BYTES 128
+QMM_API int qmm_comm_unique_id(void *id_out /* QMM_UNIQUE_ID_BYTES */);
+QMM_API int qmm_comm_init_rank(const char *name, const void *id, int nranks, int rank);
+QMM_API int qmm_comm_register(const char *name, void *nccl_comm, int nranks, int rank);
+QMM_API int qmm_comm_info(const char *name, int *nranks, int *rank);
+QMM_API int qmm_comm_destroy(const char *name);
+
+/*
+ * Row-parallel W8A8 matmul + allreduce (torch op `npu_mm_all_reduce_base`;
+ * modelled on `npu_mm_reduce_scatter_base`,
+ * MatmulReduceScatterBaseKernelNpuOpApi.cpp:22-42).  Each rank holds a K shard
+ * of x1/x2 and its own pertoken_scale; the per-rank result is rounded to
+ * out_dtype (BF16/F16) and summed over the communicator `hcom`.  bias is added
+ * on rank 0 only, so it enters the sum once.  `comm_turn` > 0 sets the number
+ * of M chunks whose allreduce overlaps the matmul of the next chunk (0 = let
+ * the library choose).  Arguments otherwise as qmm_quant_matmul.  The call
+ * returns with all work ordered on `stream`.
+ */
+QMM_API int qmm_mm_all_reduce(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_stride_k,
+                              int64_t x2_stride_n, const float *scale, int64_t scale_len,
+                              const float *pertoken_scale, const void *bias, int bias_dtype, void *out,
+                              int out_dtype, int64_t ld_out, int64_t M, int64_t N, int64_t K,
+                              const char *hcom, const char *reduce_op, int64_t comm_turn, void *workspace,
+                              size_t workspace_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QMM_B200_H_ */
