@@ -39,11 +39,30 @@ class QmmError(RuntimeError):
     pass
 
 
+def _export_nccl_path() -> None:
+    """Point the library at the NCCL build torch itself uses (it binds NCCL with dlopen)."""
+    import os
+
+    if os.environ.get("QMM_NCCL_LIB"):
+        return
+    try:
+        import nvidia.nccl  # type: ignore
+
+        for base in nvidia.nccl.__path__:
+            cand = Path(base) / "lib" / "libnccl.so.2"
+            if cand.exists():
+                os.environ["QMM_NCCL_LIB"] = str(cand)
+                return
+    except Exception:
+        pass
+
+
 def lib() -> ctypes.CDLL:
     global _lib
     if _lib is None:
         if not LIB_PATH.exists():
             raise QmmError(f"{LIB_PATH} is not built; run `python {_PKG / 'build.py'}` (there is no fallback path)")
+        _export_nccl_path()
         L = ctypes.CDLL(str(LIB_PATH), mode=ctypes.RTLD_GLOBAL)
         c = ctypes
         L.qmm_last_error.restype = c.c_char_p

@@ -1,0 +1,106 @@
+"""Call-site shim: the names existing callers use (``torch_npu.npu_quant_matmul(...)``)
+bound to this build's ``torch.ops.npu.*`` operators on CUDA tensors.
+
+It does not imitate the Ascend stack: there is no ``npu`` device, tensors live
+on ``cuda``.  Put this package's parent directory on ``sys.path`` and
+``import torch_npu``.
+
+Communicators: the reference obtains a communicator name from the process
+group (``group._get_backend(torch.device('npu')).get_hccl_comm_name(rank)``,
+test/test_custom_ops/test_mm_reduce_scatter_base.py:29-33) and passes that
+string as ``hcom``.  ``get_comm_name(group)`` is the counterpart here.
+"""
+from __future__ import annotations
+
+import ctypes
+import importlib.util
+import sys
+from pathlib import Path
+
+import torch
+
+_PKG_DIR = Path(__file__).resolve().parent.parent
+_PKG_NAME = "ascend_python_b200"
+
+
+def _load_pkg():
+    if _PKG_NAME in sys.modules:
+        return sys.modules[_PKG_NAME]
+    spec = importlib.util.spec_from_file_location(_PKG_NAME, _PKG_DIR / "__init__.py",
+                                                  submodule_search_locations=[str(_PKG_DIR)])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[_PKG_NAME] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+_pkg = _load_pkg()
+_ops = _pkg.load_ops()
+_capi = _pkg.capi
+
+
+def npu_dynamic_quant(input, *, smooth_scales=None):
+    return _ops.npu_dynamic_quant(input, smooth_scales=smooth_scales)
+
+
+def npu_quant_matmul(x1, x2, scale, *, offset=None, pertoken_scale=None, bias=None, output_dtype=None):
+    return _ops.npu_quant_matmul(x1, x2, scale, offset=offset, pertoken_scale=pertoken_scale, bias=bias,
+                                 output_dtype=output_dtype)
+
+
+def npu_weight_quant_batchmatmul(x, weight, antiquant_scale, antiquant_offset=None, quant_scale=None,
+                                 quant_offset=None, bias=None, antiquant_group_size=0):
+    return _ops.npu_weight_quant_batchmatmul(x, weight, antiquant_scale, antiquant_offset, quant_scale, quant_offset,
+                                             bias, antiquant_group_size)
+
+
+def npu_mm_all_reduce_base(x1, x2, hcom, *, reduce_op="sum", bias=None, antiquant_scale=None, antiquant_offset=None,
+                           x3=None, dequant_scale=None, pertoken_scale=None, antiquant_group_size=0, comm_turn=0):
+    return _ops.npu_mm_all_reduce_base(x1, x2, hcom, reduce_op=reduce_op, bias=bias, antiquant_scale=antiquant_scale,
+                                       antiquant_offset=antiquant_offset, x3=x3, dequant_scale=dequant_scale,
+                                       pertoken_scale=pertoken_scale, antiquant_group_size=antiquant_group_size,
+                                       comm_turn=comm_turn)
+
+
+_comm_names = {}
+
+
+def comm_name_for(group_name: str, world_size: int) -> str:
+    """Deterministic registry name of a process group's communicator."""
+    return f"qmm_comm_{group_name or 'default'}_{world_size}"
+
+
+def get_comm_name(group=None) -> str:
+    """Create (once) and register an NCCL communicator for ``group`` and return its name.
+
+    Rank 0 of the group draws the NCCL unique id; it reaches the other ranks
+    through the group's own object broadcast, so any backend works for the
+    exchange.  Every rank must call this collectively, with its GPU current.
+    """
+    import torch.distributed as dist
+
+    if not dist.is_initialized():
+        raise RuntimeError("torch.distributed is not initialized")
+    group = group if group is not None else dist.group.WORLD
+    world_size = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    name = comm_name_for(getattr(group, "group_name", "") or str(id(group) if group is not dist.group.WORLD else ""),
+                         world_size)
+    if name in _comm_names:
+        return name
+    lib = _capi.lib()
+    buf = ctypes.create_string_buffer(_capi.UNIQUE_ID_BYTES)
+    if rank == 0:
+        _capi.check(lib.qmm_comm_unique_id(buf), "qmm_comm_unique_id")
+    payload = [bytes(buf.raw) if rank == 0 else None]
+    src = dist.get_global_rank(group, 0) if group is not dist.group.WORLD else 0
+    dist.broadcast_object_list(payload, src=src, group=group)
+    uid = ctypes.create_string_buffer(payload[0], _capi.UNIQUE_ID_BYTES)
+    _capi.check(lib.qmm_comm_init_rank(name.encode(), uid, world_size, rank), "qmm_comm_init_rank")
+    _comm_names[name] = True
+    return name
+
+
+def destroy_comm(name: str) -> None:
+    if _comm_names.pop(name, None):
+        _capi.check(_capi.lib().qmm_comm_destroy(name.encode()), "qmm_comm_destroy")

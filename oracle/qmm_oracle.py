@@ -83,9 +83,9 @@ def dynamic_quant(x):
     """
     xf = _f32(x)
     shape = xf.shape
-    xf = xf.reshape(-1, shape[-1]) if xf.ndim >= 1 else xf.reshape(1, 1)
-    if xf.shape[1] == 0:
+    if xf.size == 0:
         return (torch.zeros(shape, dtype=torch.int8), torch.zeros(shape[:-1], dtype=torch.float32))
+    xf = xf.reshape(-1, shape[-1])
     amax = np.max(np.abs(xf), axis=1).astype(np.float32)
     scale = (amax / np.float32(127.0)).astype(np.float32)
     safe = np.where(scale == 0, np.float32(1.0), scale).astype(np.float32)

@@ -1,0 +1,120 @@
+"""npu_mm_all_reduce_base: a single-rank communicator on one GPU, and 2/4/8 ranks (one process per
+GPU, NCCL) when the box has that many GPUs.  Tolerance after the allreduce: rtol 1e-2 against the
+fp32 sum of the per-rank fp32 results (plus 1e-2 of the summed magnitudes as atol for cancellation)."""
+import ctypes
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+PKG_DIR = ROOT / "ascend-python_b200"
+
+
+def test_single_rank_communicator(capi, oracle, dev):
+    """nranks = 1: the op is the matmul alone; chunking over M (comm_turn) must not change a bit."""
+    sys.path.insert(0, str(PKG_DIR))
+    try:
+        import torch_npu
+    finally:
+        sys.path.pop(0)
+    lib = capi.lib()
+    uid = ctypes.create_string_buffer(capi.UNIQUE_ID_BYTES)
+    capi.check(lib.qmm_comm_unique_id(uid), "qmm_comm_unique_id")
+    capi.check(lib.qmm_comm_init_rank(b"solo", uid, 1, 0), "qmm_comm_init_rank")
+    try:
+        nr, rk = ctypes.c_int(-1), ctypes.c_int(-1)
+        capi.check(lib.qmm_comm_info(b"solo", ctypes.byref(nr), ctypes.byref(rk)), "qmm_comm_info")
+        assert (nr.value, rk.value) == (1, 0)
+        assert lib.qmm_comm_init_rank(b"solo", uid, 1, 0) == 1  # name taken
+        x, w, scale, bias = oracle.make_w8a8_inputs(640, 512, 768, seed=21)
+        q_ref, s_ref = oracle.dynamic_quant(x)
+        y_ref = oracle.quant_matmul(q_ref, w, scale, pertoken_scale=s_ref, bias=bias, output_dtype=torch.bfloat16)
+        q, s = torch_npu.npu_dynamic_quant(x.to(dev))
+        for turn in (0, 1, 3):
+            y = torch_npu.npu_mm_all_reduce_base(q, w.to(dev), "solo", reduce_op="sum", bias=bias.to(dev),
+                                                 dequant_scale=scale.to(dev), pertoken_scale=s, comm_turn=turn)
+            assert y.dtype == torch.bfloat16 and y.shape == (640, 768)
+            assert oracle.bf16_ulp_distance(y.cpu(), y_ref).max().item() <= 1
+    finally:
+        capi.check(lib.qmm_comm_destroy(b"solo"), "qmm_comm_destroy")
+    assert lib.qmm_comm_destroy(b"solo") == 5  # not found any more
+
+
+def _rank_main(rank, world, port, shapes, c2p):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    sys.path.insert(0, str(ROOT))
+    sys.path.insert(0, str(PKG_DIR))
+    import torch.distributed as dist
+    import torch_npu
+    from ascend_python_b200.sharding import shard_row_parallel
+    from oracle import qmm_oracle as O
+
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        hcom = torch_npu.get_comm_name()
+        for (M, K, N, turn) in shapes:
+            x, w, scale, bias = O.make_w8a8_inputs(M, K, N, seed=M + K + N)
+            xs, ws = shard_row_parallel(x, w, world, rank)
+            q, s = torch_npu.npu_dynamic_quant(xs.contiguous().to(dev))
+            y = torch_npu.npu_mm_all_reduce_base(q, ws.contiguous().to(dev), hcom, reduce_op="sum", bias=bias.to(dev),
+                                                 dequant_scale=scale.to(dev), pertoken_scale=s, comm_turn=turn)
+            torch.cuda.synchronize()
+            c2p.put((rank, (M, K, N, turn), y.cpu(), q.cpu(), s.cpu()))
+        dist.barrier()
+        torch_npu.destroy_comm(hcom)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_multi_rank(oracle, pkg, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    from ascend_python_b200.sharding import shard_row_parallel
+
+    shapes = [(256, 1024, 512, 0), (2048, 4096, 1024, 2), (1000, 2048, 768, 3)]
+    ctx = mp.get_context("spawn")
+    c2p = ctx.Queue()
+    port = 29700 + os.getpid() % 1000
+    env = dict(os.environ)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    try:
+        procs = [ctx.Process(target=_rank_main, args=(r, world, port, shapes, c2p)) for r in range(world)]
+        for p in procs:
+            p.start()
+        results = {}
+        for _ in range(world * len(shapes)):
+            rank, key, y, q, s = c2p.get(timeout=600)
+            results[(rank, key)] = (y, q, s)
+        for p in procs:
+            p.join(timeout=120)
+            assert p.exitcode == 0
+    finally:
+        os.environ.clear()
+        os.environ.update(env)
+    for key in shapes:
+        M, K, N, _ = key
+        x, w, scale, bias = oracle.make_w8a8_inputs(M, K, N, seed=M + K + N)
+        q_list = [results[(r, key)][1] for r in range(world)]
+        s_list = [results[(r, key)][2] for r in range(world)]
+        w_list = [shard_row_parallel(x, w, world, r)[1] for r in range(world)]
+        # every rank quantized its own shard exactly like the oracle
+        for r in range(world):
+            q_ref, s_ref = oracle.dynamic_quant(shard_row_parallel(x, w, world, r)[0].contiguous())
+            assert torch.equal(q_list[r], q_ref) and torch.equal(s_list[r], s_ref)
+        total, _ = oracle.mm_all_reduce(q_list, w_list, scale, s_list, bias=bias, output_dtype=torch.bfloat16)
+        mag = sum(np.abs(oracle.quant_matmul(q_list[r], w_list[r], scale, pertoken_scale=s_list[r],
+                                              output_dtype=torch.bfloat16).float().numpy()) for r in range(world))
+        for r in range(world):
+            y = results[(r, key)][0].float().numpy()
+            assert np.all(np.abs(y - total) <= 1e-2 * np.abs(total) + 1e-2 * mag), f"rank {r} shape {key}"
+            assert np.array_equal(y, results[(0, key)][0].float().numpy())  # all ranks hold the same result
