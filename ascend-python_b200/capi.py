@@ -120,10 +120,13 @@ def device_status(reset: bool = False) -> int:
 def dynamic_quant(x: torch.Tensor):
     """x: [..., cols] bf16/f16 CUDA tensor -> (int8 same shape, fp32 x.shape[:-1])."""
     assert x.is_cuda and x.stride(-1) == 1
-    x2 = x.reshape(-1, x.shape[-1])
+    cols = x.shape[-1]
+    rows = 1
+    for d in x.shape[:-1]:
+        rows *= d
+    x2 = x.reshape(rows, cols)
     if x2.stride(-1) != 1 and x2.numel() > 0:
         x2 = x2.contiguous()
-    rows, cols = x2.shape
     q = torch.empty((rows, cols), dtype=torch.int8, device=x.device)
     s = torch.empty((rows,), dtype=torch.float32, device=x.device)
     ld_x = x2.stride(0) if rows > 1 else max(cols, 1)

@@ -55,6 +55,7 @@ int make_tmap_2d(CUtensorMap *map, const void *base, int elem_bytes, uint64_t in
 enum : uint32_t {
     DEV_STATUS_OK = 0,
     DEV_STATUS_WAIT_TIMEOUT = 0x10000,  // low 16 bits: which wait gave up
+    DEV_STATUS_SMEM_MISALIGNED = 0x20000,  // dynamic shared memory not 1024-byte aligned: kernel did nothing
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -134,6 +135,30 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1)
         : "memory");
+}
+
+// 2-D tiled store shared (this CTA) -> global, tracked by the thread's bulk async-group.
+// Out-of-range parts of the box are clipped.  c0 * element size must be a multiple of 16
+// and no coordinate may be negative.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *m, uint32_t smem_src, int32_t c0, int32_t c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(m)),
+                 "r"(smem_src), "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Wait until at most N of this thread's bulk groups still read their shared-memory source.
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void tma_store_wait_all() {
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+// Make generic-proxy writes to shared memory visible to the async proxy (TMA).
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
 // ---- tcgen05 / TMEM ---------------------------------------------------------

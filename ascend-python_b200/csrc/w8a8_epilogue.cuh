@@ -109,6 +109,121 @@ __device__ __forceinline__ void epilogue_row_segment(const EpilogueParams &p, in
     }
 }
 
+// ---------------------------------------------------------------------------
+// Epilogue of one warp through shared memory and TMA stores.
+//
+// The warp owns 32 accumulator rows (TMEM lanes) of a tile that is TILE_N
+// columns wide.  It walks the tile in chunks whose rows are 128 bytes of
+// output (64 columns of bf16/f16, 32 of int32): TMEM -> registers -> fp32
+// dequantization -> a 4 KiB staging buffer laid out with the 128-byte swizzle
+// (bank-conflict free 16-byte stores) -> one TMA store per chunk.  Two staging
+// buffers alternate so that the store of chunk c overlaps the math of c+1.
+// Per-column scale and bias of a chunk are fetched once per warp (coalesced)
+// into a small shared array and read back as broadcasts.
+//
+// `stage` points to this warp's 8 KiB staging area (1024-byte aligned),
+// `colbuf` to its 2*64 floats.  `chunk_counter` persists across tiles: it
+// numbers the warp's TMA stores so that buffer reuse can be fenced.
+// ---------------------------------------------------------------------------
+template <typename OutT>
+struct EpiChunk {
+    static constexpr int kCols = 128 / static_cast<int>(sizeof(OutT));  // columns per 128-byte row
+};
+
+template <typename OutT, int TILE_N>
+__device__ __forceinline__ void epilogue_warp_tile_tma(const EpilogueParams &p, const CUtensorMap *tmap_out,
+                                                       uint32_t taddr_warp, int64_t m_warp0, int64_t n_tile0,
+                                                       uint8_t *stage, float *colbuf, uint32_t &chunk_counter) {
+    constexpr int CC = EpiChunk<OutT>::kCols;
+    const int lane = threadIdx.x & 31;
+    const int64_t m = m_warp0 + lane;
+    const bool is_int = (sizeof(OutT) == 4);
+    const bool has_pt = !is_int && (p.pertoken_scale != nullptr);
+    const bool has_bias = (p.bias != nullptr) && (is_int ? p.bias_dtype == QMM_DTYPE_I32
+                                                         : (p.bias_dtype != QMM_DTYPE_NONE &&
+                                                            p.bias_dtype != QMM_DTYPE_I32));
+    const float pt = (has_pt && m < p.M) ? __ldg(p.pertoken_scale + m) : 1.0f;
+    const uint32_t stage_u32 = smem_u32(stage);
+    if (m_warp0 >= p.M) return;  // the warp's rows are all padding
+
+#pragma unroll 1
+    for (int c = 0; c < TILE_N / CC; ++c) {
+        const int64_t n0 = n_tile0 + static_cast<int64_t>(c) * CC;
+        if (n0 >= p.N) break;
+        const uint32_t buf = chunk_counter & 1;
+        // the TMA store that last read this buffer (two chunks ago) must have finished reading it
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+
+        // per-column constants of this chunk -> shared (coalesced), as fp32 bit patterns
+#pragma unroll
+        for (int i = lane; i < CC; i += 32) {
+            const int64_t n = n0 + i;
+            float sc = 1.0f, bi = 0.0f;
+            if (n < p.N) {
+                if (is_int) {
+                    if (has_bias) bi = __int_as_float(__ldg(static_cast<const int32_t *>(p.bias) + n));
+                } else {
+                    sc = p.scale_is_scalar ? __ldg(p.scale) : __ldg(p.scale + n);
+                    if (has_bias) bi = load_bias_f32(p, n);
+                }
+            }
+            colbuf[i] = sc;
+            colbuf[64 + i] = bi;
+        }
+        __syncwarp();
+
+        uint8_t *dst_row = stage + buf * 4096 + lane * 128;
+#pragma unroll
+        for (int h = 0; h < CC / 32; ++h) {
+            uint32_t acc[32];
+            tmem_ld_32x32(taddr_warp + c * CC + h * 32, acc);
+            tmem_ld_wait();
+            if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                    const float4 b4 = *reinterpret_cast<const float4 *>(colbuf + 64 + h * 32 + j);
+                    int4 v;
+                    v.x = static_cast<int32_t>(acc[j + 0]) + __float_as_int(b4.x);
+                    v.y = static_cast<int32_t>(acc[j + 1]) + __float_as_int(b4.y);
+                    v.z = static_cast<int32_t>(acc[j + 2]) + __float_as_int(b4.z);
+                    v.w = static_cast<int32_t>(acc[j + 3]) + __float_as_int(b4.w);
+                    const int chunk16 = (h * 32 + j) / 4;  // 16-byte chunk index within the 128-byte row
+                    *reinterpret_cast<int4 *>(dst_row + ((chunk16 ^ (lane & 7)) << 4)) = v;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                    float f[8];
+#pragma unroll
+                    for (int q4 = 0; q4 < 2; ++q4) {
+                        const float4 s4 = *reinterpret_cast<const float4 *>(colbuf + h * 32 + j + q4 * 4);
+                        const float4 b4 = *reinterpret_cast<const float4 *>(colbuf + 64 + h * 32 + j + q4 * 4);
+                        f[q4 * 4 + 0] = dequant_one(static_cast<int32_t>(acc[j + q4 * 4 + 0]), s4.x, pt, has_pt, b4.x, has_bias);
+                        f[q4 * 4 + 1] = dequant_one(static_cast<int32_t>(acc[j + q4 * 4 + 1]), s4.y, pt, has_pt, b4.y, has_bias);
+                        f[q4 * 4 + 2] = dequant_one(static_cast<int32_t>(acc[j + q4 * 4 + 2]), s4.z, pt, has_pt, b4.z, has_bias);
+                        f[q4 * 4 + 3] = dequant_one(static_cast<int32_t>(acc[j + q4 * 4 + 3]), s4.w, pt, has_pt, b4.w, has_bias);
+                    }
+                    uint4 w;
+                    w.x = pack2<OutT>(f[0], f[1]);
+                    w.y = pack2<OutT>(f[2], f[3]);
+                    w.z = pack2<OutT>(f[4], f[5]);
+                    w.w = pack2<OutT>(f[6], f[7]);
+                    const int chunk16 = (h * 32 + j) / 8;
+                    *reinterpret_cast<uint4 *>(dst_row + ((chunk16 ^ (lane & 7)) << 4)) = w;
+                }
+            }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            tma_store_2d(tmap_out, stage_u32 + buf * 4096, static_cast<int32_t>(n0), static_cast<int32_t>(m_warp0));
+            tma_store_commit();
+        }
+        ++chunk_counter;
+    }
+}
+
 // One element (used by kernels whose threads own a column of the accumulator).
 template <typename OutT>
 __device__ __forceinline__ void epilogue_one(const EpilogueParams &p, int64_t m, int64_t n, int32_t acc) {

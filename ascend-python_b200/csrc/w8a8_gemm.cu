@@ -50,7 +50,14 @@ struct TileSmemTail {
     uint32_t abort_flag;
 };
 
-constexpr size_t kTileSmemBytes = 1024 /*alignment slack*/ + kStages * kStageBytes + sizeof(TileSmemTail);
+constexpr int kEpiWarps = 4;
+constexpr int kEpiStageBytes = 2 * 4096;  // per warp: two 32-row x 128-byte staging buffers
+constexpr int kEpiColFloats = 128;        // per warp: 64 scales + 64 biases
+
+// dynamic shared memory: [operand ring][epilogue staging][per-column constants][barriers]
+constexpr size_t kTileSmemBytes = kStages * kStageBytes + kEpiWarps * kEpiStageBytes +
+                                  kEpiWarps * kEpiColFloats * sizeof(float) + sizeof(TileSmemTail);
+static_assert(kTileSmemBytes <= 232448, "tile kernel exceeds the 227 KiB of shared memory a CTA may use");
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int &m_blk, int &n_blk) {
     const int per_group = kGroupM * tiles_n;
@@ -65,11 +72,19 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 template <typename OutT, bool B_MN_MAJOR>
 __global__ void __launch_bounds__(kTileThreads, 1)
 w8a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 EpilogueParams ep, int K, uint32_t *status) {
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t *smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
-    TileSmemTail *tail = reinterpret_cast<TileSmemTail *>(smem_aligned + kStages * kStageBytes);
+                 const __grid_constant__ CUtensorMap tmap_out, EpilogueParams ep, int K, int use_tma_store,
+                 uint32_t *status) {
+    // The 128-byte swizzle of TMA and of the MMA descriptors needs 1024-byte aligned tiles.
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t smem_base = smem_u32(smem_raw);
+    if ((smem_base & 1023u) != 0) {
+        if (threadIdx.x == 0 && status != nullptr) atomicMax(status, DEV_STATUS_SMEM_MISALIGNED);
+        return;
+    }
+    uint8_t *smem_aligned = smem_raw;
+    uint8_t *epi_stage = smem_aligned + kStages * kStageBytes;
+    float *epi_cols = reinterpret_cast<float *>(epi_stage + kEpiWarps * kEpiStageBytes);
+    TileSmemTail *tail = reinterpret_cast<TileSmemTail *>(epi_cols + kEpiWarps * kEpiColFloats);
     volatile uint32_t *abort_flag = &tail->abort_flag;
 
     const int warp = threadIdx.x >> 5;
@@ -185,8 +200,12 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     } else {
         // ---------------- epilogue warps ----------------
         const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
+        uint8_t *my_stage = epi_stage + quarter * kEpiStageBytes;
+        float *my_cols = epi_cols + quarter * kEpiColFloats;
+        uint32_t chunk_counter = 0;
         int local = 0;
         bool ok = true;
+        if (lane == 0 && use_tma_store) tma_prefetch_desc(&tmap_out);
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
             int m_blk, n_blk;
             tile_coords(tile, tiles_m, tiles_n, m_blk, n_blk);
@@ -195,19 +214,27 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             ok = mbar_wait(smem_u32(&tail->tmem_full[buf]), buf_phase, abort_flag, 4);
             if (!ok) break;
             tc_fence_after();
-            const int64_t m = static_cast<int64_t>(m_blk) * kBM + quarter * 32 + lane;
+            const int64_t m_warp0 = static_cast<int64_t>(m_blk) * kBM + quarter * 32;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBN;
+            if (use_tma_store) {
+                epilogue_warp_tile_tma<OutT, kBN>(ep, &tmap_out, taddr, m_warp0, static_cast<int64_t>(n_blk) * kBN,
+                                                  my_stage, my_cols, chunk_counter);
+            } else {
 #pragma unroll 1
-            for (int c = 0; c < kBN / 32; ++c) {
-                uint32_t acc[32];
-                tmem_ld_32x32(taddr + c * 32, acc);
-                tmem_ld_wait();
-                epilogue_row_segment<OutT, 32>(ep, m, static_cast<int64_t>(n_blk) * kBN + c * 32, acc);
+                for (int c = 0; c < kBN / 32; ++c) {
+                    uint32_t acc[32];
+                    tmem_ld_32x32(taddr + c * 32, acc);
+                    tmem_ld_wait();
+                    epilogue_row_segment<OutT, 32>(ep, m_warp0 + lane, static_cast<int64_t>(n_blk) * kBN + c * 32, acc);
+                }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&tail->tmem_empty[buf]));
         }
+        // all of this warp's TMA stores must have left shared memory before the CTA exits
+        if (lane == 0) tma_store_wait_all<0>();
+        __syncwarp();
     }
 
     // ---------------- teardown ----------------
@@ -302,6 +329,17 @@ int launch_tile(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk
                           static_cast<uint64_t>(x2_sn), kBK, kBN, true);
     }
     if (rc != QMM_OK) return rc;
+    // The epilogue stores through TMA when the output meets the 16-byte rules; it writes
+    // straight from registers otherwise.
+    constexpr int kElt = static_cast<int>(sizeof(OutT));
+    CUtensorMap tout = ta;
+    int use_tma_store = 0;
+    if ((reinterpret_cast<uintptr_t>(ep.out) & 15) == 0 && ((ep.ld_out * kElt) & 15) == 0) {
+        rc = make_tmap_2d(&tout, ep.out, kElt, static_cast<uint64_t>(ep.N), static_cast<uint64_t>(ep.M),
+                          static_cast<uint64_t>(ep.ld_out), 128 / kElt, 32, true);
+        if (rc != QMM_OK) return rc;
+        use_tma_store = 1;
+    }
     const int tiles = static_cast<int>(((ep.M + kBM - 1) / kBM) * ((ep.N + kBN - 1) / kBN));
     int ctas = sm_count() - g_sm_reserve;
     if (ctas < 1) ctas = 1;
@@ -310,7 +348,7 @@ int launch_tile(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk
     auto kern = mn_major ? w8a8_tile_kernel<OutT, true> : w8a8_tile_kernel<OutT, false>;
     QMM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(kTileSmemBytes)));
-    kern<<<grid, kTileThreads, kTileSmemBytes, stream>>>(ta, tb, ep, static_cast<int>(K), status);
+    kern<<<grid, kTileThreads, kTileSmemBytes, stream>>>(ta, tb, tout, ep, static_cast<int>(K), use_tma_store, status);
     QMM_CUDA_OK(cudaGetLastError());
     return QMM_OK;
 }

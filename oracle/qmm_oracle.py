@@ -248,3 +248,37 @@ def make_w4a16_inputs(M: int, K: int, N: int, seed: int, *, group=128, dtype=tor
     scale = torch.empty((ng, N), dtype=torch.float32).uniform_(5e-3, 2e-2, generator=g).to(dtype)
     offset = torch.empty((ng, N), dtype=torch.float32).uniform_(-1.0, 1.0, generator=g).to(dtype)
     return x, packed, scale, offset
+
+
+# ---------------------------------------------------------------------------
+# the reference-style CPU path (timed as the CPU baseline)
+# ---------------------------------------------------------------------------
+
+
+def cpu_path_w8a8(x: torch.Tensor, w_f32: torch.Tensor, scale: torch.Tensor, bias, output_dtype=torch.bfloat16):
+    """dynamic quant + W8A8 matmul + dequantization with multi-threaded torch CPU operators.
+
+    This is the computation the reference's tests run on the host as their golden
+    (``torch.matmul(x1.to(torch.float), x2.to(torch.float))``,
+    test/test_custom_ops/test_mm_reduce_scatter_base.py:74): fp32 BLAS on int8-valued
+    operands.  The product is evaluated in K chunks of 1024 so that every fp32 partial sum
+    is an exact integer (1024 * 127 * 128 < 2^24) and the chunks are added in int32; the
+    result equals ``quant_matmul(dynamic_quant(x), w, ...)`` bit for bit.
+    `w_f32` is the int8 weight already converted to float32 (weights are static).
+    """
+    xf = x.float()
+    amax = xf.abs().amax(dim=-1)
+    s = amax / 127.0
+    safe = torch.where(s == 0, torch.ones_like(s), s)
+    q = torch.clamp(torch.round(xf / safe[:, None]), -128, 127)
+    q = torch.where(s[:, None] == 0, torch.zeros_like(q), q)
+    K = q.shape[1]
+    acc = None
+    for k0 in range(0, K, 1024):
+        part = torch.matmul(q[:, k0:k0 + 1024], w_f32[k0:k0 + 1024]).to(torch.int32)
+        acc = part if acc is None else acc + part
+    v = acc.to(torch.float32) * scale[None, :]
+    v = v * s[:, None]
+    if bias is not None:
+        v = v + bias.float()[None, :]
+    return v.to(output_dtype), q.to(torch.int8), s

@@ -88,5 +88,5 @@ def test_full_size_properties(capi, oracle, dev):
         assert torch.equal(q[rows.to(dev)].cpu(), q_ref) and torch.equal(s[rows.to(dev)].cpu(), s_ref)
         assert torch.all(q.abs().amax(dim=1) == 127)
         err = (x.float() - q.float() * s[:, None]).abs()
-        assert torch.all(err <= s[:, None] * 0.5000005)
+        assert torch.all(err <= s[:, None] * 0.50002)  # half a step + fp32 rounding of x/s and q*s
         del x, err
