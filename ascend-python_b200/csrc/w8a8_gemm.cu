@@ -24,6 +24,11 @@ namespace qmm {
 // SMs the persistent tile kernel leaves idle (set around launches that overlap a collective).
 static thread_local int g_sm_reserve = 0;
 void set_sm_reserve(int sms) { g_sm_reserve = sms < 0 ? 0 : sms; }
+int pair_sm_reserve() { return g_sm_reserve; }
+
+// Implemented in w8a8_gemm_pair.cu
+int launch_pair(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
+                const struct EpilogueParams &ep, int out_dtype, int64_t K, cudaStream_t stream);
 
 namespace {
 
@@ -395,7 +400,7 @@ int quant_matmul_dispatch(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int
         else
             algo = QMM_ALGO_TCGEN05_TILE;
     }
-    if ((algo == QMM_ALGO_TCGEN05_TILE || algo == QMM_ALGO_TCGEN05_STREAMK) && !tma_ok)
+    if ((algo == QMM_ALGO_TCGEN05_TILE || algo == QMM_ALGO_TCGEN05_STREAMK || algo == QMM_ALGO_TCGEN05_PAIR) && !tma_ok)
         return fail(QMM_ERR_UNSUPPORTED,
                     "qmm_quant_matmul: tcgen05 kernels need 16-byte aligned operands and row pitches");
     switch (algo) {
@@ -408,6 +413,8 @@ int quant_matmul_dispatch(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int
                 default:
                     return launch_tile<int32_t>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, stream);
             }
+        case QMM_ALGO_TCGEN05_PAIR:
+            return launch_pair(x1, ld_x1, x2, x2_sk, x2_sn, ep, out_dtype, K, stream);
         case QMM_ALGO_TCGEN05_STREAMK:
             return launch_streamk(x1, ld_x1, x2, x2_sk, x2_sn, ep, out_dtype, K, workspace, workspace_bytes, stream);
         case QMM_ALGO_SIMT:

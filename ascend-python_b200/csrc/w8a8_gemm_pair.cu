@@ -1,0 +1,300 @@
+// W8A8 prefill matmul on CTA pairs (tcgen05 cta_group::2).
+//
+// Two CTAs of a cluster, on the two SMs of a TPC, share one 256x256 output
+// tile: each loads its own 128 rows of A and one 128-column half of B per
+// k-block (32 KiB per stage and CTA instead of 48 KiB for a 128x256 tile of its
+// own), the leader CTA issues one 256x256x32 MMA for the pair, and each CTA
+// receives its 128 rows of the int32 accumulator in its own TMEM.  Per output
+// element the pair moves a third less data from L2 to shared memory and keeps
+// six stages in flight instead of four, which is what the int8 MMA rate needs.
+//
+// Synchronisation (s = stage, b = accumulator buffer):
+//   full[s]       leader's barrier; both CTAs' TMA loads count their bytes on it
+//   empty[s]      one per CTA; the leader's tcgen05.commit arrives on both
+//   tmem_full[b]  one per CTA; the leader's tcgen05.commit arrives on both
+//   tmem_empty[b] leader's barrier; the 4+4 epilogue warps of the pair arrive on it
+// No TMA load uses multicast; every wait is bounded (see mbar_wait).
+#include "qmm_common.cuh"
+#include "w8a8_epilogue.cuh"
+
+namespace qmm {
+
+int pair_sm_reserve();  // SMs to leave idle (set by callers that overlap a collective)
+
+namespace {
+
+constexpr int kPM = 128;   // rows per CTA
+constexpr int kPN = 256;   // columns of the pair's tile
+constexpr int kPK = 128;   // k elements per stage
+constexpr int kPStages = 6;
+constexpr int kPAStageBytes = kPM * kPK;
+constexpr int kPBStageBytes = (kPN / 2) * kPK;
+constexpr int kPStageBytes = kPAStageBytes + kPBStageBytes;  // per CTA
+constexpr int kPThreads = 192;
+constexpr int kPGroupM = 8;  // pair-tiles (256 rows each) per rasterization group
+constexpr uint32_t kPTmemCols = 512;
+constexpr int kPEpiWarps = 4;
+constexpr int kPEpiStageBytes = 2 * 4096;
+constexpr int kPEpiColFloats = 128;
+
+struct PairSmemTail {
+    uint64_t full[kPStages];
+    uint64_t empty[kPStages];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+constexpr size_t kPairSmemBytes = kPStages * kPStageBytes + kPEpiWarps * kPEpiStageBytes +
+                                  kPEpiWarps * kPEpiColFloats * sizeof(float) + sizeof(PairSmemTail);
+static_assert(kPairSmemBytes <= 232448, "pair kernel exceeds the 227 KiB of shared memory a CTA may use");
+
+__device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int &m_blk, int &n_blk) {
+    const int per_group = kPGroupM * tiles_n;
+    const int g = tile / per_group;
+    const int first_m = g * kPGroupM;
+    const int rows = min(kPGroupM, tiles_m - first_m);
+    const int r = tile - g * per_group;
+    m_blk = first_m + r % rows;
+    n_blk = r / rows;
+}
+
+template <typename OutT, bool B_MN_MAJOR>
+__global__ void __launch_bounds__(kPThreads, 1)
+w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_out, EpilogueParams ep, int K, int use_tma_store,
+                 uint32_t *status) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t smem_base = smem_u32(smem_raw);
+    const uint32_t cta_rank = cluster_ctarank();  // 0 = leader
+    const bool leader = (cta_rank == 0);
+    uint8_t *epi_stage = smem_raw + kPStages * kPStageBytes;
+    float *epi_cols = reinterpret_cast<float *>(epi_stage + kPEpiWarps * kPEpiStageBytes);
+    PairSmemTail *tail = reinterpret_cast<PairSmemTail *>(epi_cols + kPEpiWarps * kPEpiColFloats);
+    volatile uint32_t *abort_flag = &tail->abort_flag;
+    // both CTAs of a pair see the same alignment, so this exit is taken by both or by none
+    if ((smem_base & 1023u) != 0) {
+        if (threadIdx.x == 0 && status != nullptr) atomicMax(status, DEV_STATUS_SMEM_MISALIGNED);
+        return;
+    }
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int tiles_m = static_cast<int>((ep.M + 2 * kPM - 1) / (2 * kPM));
+    const int tiles_n = static_cast<int>((ep.N + kPN - 1) / kPN);
+    const int num_tiles = tiles_m * tiles_n;
+    const int num_kb = (K + kPK - 1) / kPK;
+    const int pair_id = blockIdx.x >> 1;
+    const int num_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kPStages; ++s) {
+            mbar_init(smem_u32(&tail->full[s]), 1);
+            mbar_init(smem_u32(&tail->empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&tail->tmem_full[b]), 1);
+            mbar_init(smem_u32(&tail->tmem_empty[b]), 2 * kPEpiWarps);
+        }
+        tail->abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 0 && lane == 0) {
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(smem_u32(&tail->tmem_base), kPTmemCols);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // the peer's barriers are initialised before anything signals them
+    tc_fence_after();
+    const uint32_t tmem_base = tail->tmem_base;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs) ----------------
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+            int m_blk, n_blk;
+            pair_tile_coords(tile, tiles_m, tiles_n, m_blk, n_blk);
+            const int m0 = m_blk * 2 * kPM + static_cast<int>(cta_rank) * kPM;
+            const int n0 = n_blk * kPN + static_cast<int>(cta_rank) * (kPN / 2);
+            for (int kb = 0; kb < num_kb; ++kb) {
+                ok = mbar_wait(smem_u32(&tail->empty[stage]), phase ^ 1, abort_flag, 0x21);
+                if (!ok) break;
+                if (lane == 0) {
+                    const uint32_t full_local = smem_u32(&tail->full[stage]);
+                    const uint32_t full_leader = map_to_cta(full_local, 0);
+                    const uint32_t sa = smem_base + stage * kPStageBytes;
+                    const uint32_t sb = sa + kPAStageBytes;
+                    if (leader) mbar_expect_tx(full_local, 2 * kPStageBytes);
+                    tma_load_2d_pair(sa, &tmap_a, kb * kPK, m0, full_leader);
+                    if (B_MN_MAJOR)
+                        tma_load_2d_pair(sb, &tmap_b, n0, kb * kPK, full_leader);  // [128 k-rows][128 n-bytes]
+                    else
+                        tma_load_2d_pair(sb, &tmap_b, kb * kPK, n0, full_leader);  // [128 n-rows][128 k-bytes]
+                }
+                __syncwarp();
+                if (++stage == kPStages) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader CTA only) ----------------
+        if (leader) {
+            constexpr uint32_t idesc = make_idesc(/*c=s32*/ 2, 1, 1, /*a K-major*/ 0, B_MN_MAJOR ? 1u : 0u, 2 * kPM, kPN);
+            uint32_t stage = 0, phase = 0;
+            int local = 0;
+            bool ok = true;
+            for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++local) {
+                const uint32_t buf = local & 1;
+                const uint32_t buf_phase = (local >> 1) & 1;
+                ok = mbar_wait(smem_u32(&tail->tmem_empty[buf]), buf_phase ^ 1, abort_flag, 0x22);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * kPN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = mbar_wait(smem_u32(&tail->full[stage]), phase, abort_flag, 0x23);
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (lane == 0) {
+                        const uint32_t sa = smem_base + stage * kPStageBytes;
+                        const uint32_t sb = sa + kPAStageBytes;
+#pragma unroll
+                        for (int k = 0; k < kPK / 32; ++k) {
+                            const uint64_t adesc = make_smem_desc_sw128(sa + k * 32, 16, 1024);
+                            const uint64_t bdesc = B_MN_MAJOR ? make_smem_desc_sw128(sb + k * 4096, 1024, 1024)
+                                                              : make_smem_desc_sw128(sb + k * 32, 16, 1024);
+                            mma_i8_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        }
+                        tc_commit_pair(smem_u32(&tail->empty[stage]), 0x3);
+                    }
+                    __syncwarp();
+                    if (++stage == kPStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (ok && lane == 0) tc_commit_pair(smem_u32(&tail->tmem_full[buf]), 0x3);
+                __syncwarp();
+            }
+        }
+    } else {
+        // ---------------- epilogue warps (both CTAs) ----------------
+        const int quarter = warp & 3;
+        uint8_t *my_stage = epi_stage + quarter * kPEpiStageBytes;
+        float *my_cols = epi_cols + quarter * kPEpiColFloats;
+        uint32_t chunk_counter = 0;
+        int local = 0;
+        bool ok = true;
+        if (lane == 0 && use_tma_store) tma_prefetch_desc(&tmap_out);
+        for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++local) {
+            int m_blk, n_blk;
+            pair_tile_coords(tile, tiles_m, tiles_n, m_blk, n_blk);
+            const uint32_t buf = local & 1;
+            const uint32_t buf_phase = (local >> 1) & 1;
+            ok = mbar_wait(smem_u32(&tail->tmem_full[buf]), buf_phase, abort_flag, 0x24);
+            if (!ok) break;
+            tc_fence_after();
+            const int64_t m_warp0 = static_cast<int64_t>(m_blk) * 2 * kPM + cta_rank * kPM + quarter * 32;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kPN;
+            if (use_tma_store) {
+                epilogue_warp_tile_tma<OutT, kPN>(ep, &tmap_out, taddr, m_warp0, static_cast<int64_t>(n_blk) * kPN,
+                                                  my_stage, my_cols, chunk_counter);
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < kPN / 32; ++c) {
+                    uint32_t acc[32];
+                    tmem_ld_32x32(taddr + c * 32, acc);
+                    tmem_ld_wait();
+                    epilogue_row_segment<OutT, 32>(ep, m_warp0 + lane, static_cast<int64_t>(n_blk) * kPN + c * 32, acc);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tail->tmem_empty[buf]), 0));
+        }
+        if (lane == 0) tma_store_wait_all<0>();
+        __syncwarp();
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && tail->abort_flag != 0 && status != nullptr) atomicMax(status, tail->abort_flag);
+    cluster_sync_all();  // nobody signals a CTA that already left; both are done with TMEM
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, kPTmemCols);
+    }
+}
+
+template <typename OutT>
+int launch_pair_t(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
+                  const EpilogueParams &ep, int64_t K, cudaStream_t stream) {
+    CUtensorMap ta, tb;
+    int rc = make_tmap_2d(&ta, x1, 1, static_cast<uint64_t>(K), static_cast<uint64_t>(ep.M),
+                          static_cast<uint64_t>(ld_x1), kPK, kPM, true);
+    if (rc != QMM_OK) return rc;
+    const bool mn_major = (x2_sn == 1);
+    if (mn_major)
+        rc = make_tmap_2d(&tb, x2, 1, static_cast<uint64_t>(ep.N), static_cast<uint64_t>(K),
+                          static_cast<uint64_t>(x2_sk), 128, kPK, true);
+    else
+        rc = make_tmap_2d(&tb, x2, 1, static_cast<uint64_t>(K), static_cast<uint64_t>(ep.N),
+                          static_cast<uint64_t>(x2_sn), kPK, kPN / 2, true);
+    if (rc != QMM_OK) return rc;
+    constexpr int kElt = static_cast<int>(sizeof(OutT));
+    CUtensorMap tout = ta;
+    int use_tma_store = 0;
+    if ((reinterpret_cast<uintptr_t>(ep.out) & 15) == 0 && ((ep.ld_out * kElt) & 15) == 0) {
+        rc = make_tmap_2d(&tout, ep.out, kElt, static_cast<uint64_t>(ep.N), static_cast<uint64_t>(ep.M),
+                          static_cast<uint64_t>(ep.ld_out), 128 / kElt, 32, true);
+        if (rc != QMM_OK) return rc;
+        use_tma_store = 1;
+    }
+    const int tiles = static_cast<int>(((ep.M + 2 * kPM - 1) / (2 * kPM)) * ((ep.N + kPN - 1) / kPN));
+    int pairs = (sm_count() - pair_sm_reserve()) / 2;
+    if (pairs < 1) pairs = 1;
+    if (tiles < pairs) pairs = tiles;
+    uint32_t *status = device_status_word();
+    auto kern = mn_major ? w8a8_pair_kernel<OutT, true> : w8a8_pair_kernel<OutT, false>;
+    QMM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(kPairSmemBytes)));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+    cfg.blockDim = dim3(kPThreads);
+    cfg.dynamicSmemBytes = kPairSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    QMM_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ta, tb, tout, ep, static_cast<int>(K), use_tma_store, status));
+    return QMM_OK;
+}
+
+}  // namespace
+
+int launch_pair(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
+                const EpilogueParams &ep, int out_dtype, int64_t K, cudaStream_t stream) {
+    switch (out_dtype) {
+        case QMM_DTYPE_BF16:
+            return launch_pair_t<__nv_bfloat16>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, stream);
+        case QMM_DTYPE_F16:
+            return launch_pair_t<__half>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, stream);
+        default:
+            return launch_pair_t<int32_t>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, stream);
+    }
+}
+
+}  // namespace qmm
