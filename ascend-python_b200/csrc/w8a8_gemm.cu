@@ -397,6 +397,8 @@ int quant_matmul_dispatch(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int
         else if (streamk_supported(ep.M, ep.N, K, x2_sn) && workspace != nullptr &&
                  workspace_bytes >= streamk_workspace_bytes(ep.M, ep.N, K))
             algo = QMM_ALGO_TCGEN05_STREAMK;
+        else if (ep.M > 128)
+            algo = QMM_ALGO_TCGEN05_PAIR;  // a few percent ahead of the one-CTA kernel under the power cap
         else
             algo = QMM_ALGO_TCGEN05_TILE;
     }
