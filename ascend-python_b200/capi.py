@@ -26,8 +26,9 @@ EXPORTED_SYMBOLS = (
     "qmm_last_error", "qmm_version", "qmm_device_status", "qmm_dynamic_quant",
     "qmm_quant_matmul_workspace_size", "qmm_quant_matmul", "qmm_weight_quant_batchmatmul",
     "qmm_comm_unique_id", "qmm_comm_init_rank", "qmm_comm_register", "qmm_comm_info", "qmm_comm_destroy",
-    "qmm_mm_all_reduce",
+    "qmm_mm_all_reduce", "qmm_quant_matmul_decode_noalloc",
 )
+NOALLOC_SCRATCH_BYTES = 16 << 20
 
 _TORCH_TO_QMM = {torch.bfloat16: DTYPE_BF16, torch.float16: DTYPE_F16, torch.float32: DTYPE_F32,
                  torch.int32: DTYPE_I32}
@@ -75,6 +76,11 @@ def lib() -> ctypes.CDLL:
         L.qmm_quant_matmul.argtypes = [c.c_void_p, c.c_int64, c.c_void_p, c.c_int64, c.c_int64, c.c_void_p, c.c_int64,
                                        c.c_void_p, c.c_void_p, c.c_int, c.c_void_p, c.c_int, c.c_int64, c.c_int64,
                                        c.c_int64, c.c_int64, c.c_int, c.c_void_p, c.c_size_t, c.c_void_p]
+        L.qmm_quant_matmul_decode_noalloc.argtypes = [c.c_void_p, c.c_int64, c.c_void_p, c.c_int64, c.c_int64,
+                                                      c.c_void_p, c.c_int64, c.c_void_p, c.c_void_p, c.c_int,
+                                                      c.c_void_p, c.c_int, c.c_int64, c.c_int64, c.c_int64,
+                                                      c.c_int64, c.c_void_p]
+        L.qmm_quant_matmul_decode_noalloc.restype = c.c_int
         L.qmm_weight_quant_batchmatmul.argtypes = [c.c_void_p, c.c_int, c.c_int64, c.c_void_p, c.c_int64, c.c_void_p,
                                                    c.c_void_p, c.c_int64, c.c_void_p, c.c_void_p, c.c_int64,
                                                    c.c_int64, c.c_int64, c.c_int64, c.c_void_p]

@@ -12,6 +12,8 @@
 // accumulator with red.global.add (integer addition: the result does not
 // depend on arrival order) and the CTA that completes the tile's k-block count
 // applies the epilogue and re-zeroes the scratch for the next call.
+#include <mutex>
+
 #include "qmm_common.cuh"
 #include "w8a8_epilogue.cuh"
 
@@ -366,3 +368,149 @@ int launch_streamk(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2
 }
 
 }  // namespace qmm
+
+// ---------------------------------------------------------------------------
+// Decode matmul for callers that cannot allocate device memory.
+//
+// Some hosts of this library run where cudaMalloc is off limits: inside a
+// serving loop whose memory was carved up at start-up and handed out by the
+// host's own arena, in a plugin whose contract forbids allocation after
+// initialisation, or on a thread that must never take the allocator's locks.
+// The regular entry point needs a scratch buffer from its caller (and the
+// operator host code takes that from the framework allocator).  This variant
+// brings its own: the split-K partial sums and tile counters live in a
+// fixed-size array that is part of the library image, so the call itself
+// allocates nothing, on the device or on the host.
+// ---------------------------------------------------------------------------
+namespace qmm {
+namespace {
+
+// Scratch of the no-allocation entry point.  Every device that loads the library
+// holds these 16 MiB until the process exits.
+static __device__ __align__(256) uint8_t g_noalloc_scratch[QMM_NOALLOC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mutex;
+void *g_noalloc_ptr[kMaxDevices] = {};
+
+// Device address of g_noalloc_scratch on the current device.  In host code the
+// array's name is only a handle for the runtime, not an address a kernel could
+// use, so the address is looked up once per device (with that device current).
+int noalloc_scratch_address(void **out) {
+    int dev = 0;
+    QMM_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(QMM_ERR_UNSUPPORTED, "device ordinal beyond 63");
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_ptr[dev] == nullptr) {
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            return fail(QMM_ERR_CUDA, std::string("cudaGetSymbolAddress(g_noalloc_scratch): ") + cudaGetErrorString(e));
+        g_noalloc_ptr[dev] = p;
+    }
+    *out = g_noalloc_ptr[dev];
+    return QMM_OK;
+}
+
+template <typename OutT>
+int launch_streamk_noalloc_t(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
+                             const EpilogueParams &ep, int64_t K, void *scratch, cudaStream_t stream) {
+    SkParams p;
+    p.ep = ep;
+    p.K = static_cast<int>(K);
+    p.mpad = mpad_of(ep.M);
+    p.stage_bytes = kSkABytes + p.mpad * kSkBK;
+    int stages = static_cast<int>((kSkSmemBudget - 1024 - sizeof(SkSmemTail)) / p.stage_bytes);
+    p.stages = stages > kSkMaxStages ? kSkMaxStages : stages;
+    p.tiles_n = static_cast<int>((ep.N + kSkTileN - 1) / kSkTileN);
+    p.kblocks = static_cast<int>((K + kSkBK - 1) / kSkBK);
+    const size_t acc_bytes = static_cast<size_t>(p.tiles_n) * p.mpad * kSkTileN * sizeof(int32_t);
+    p.ws_acc = static_cast<int32_t *>(scratch);
+    p.ws_count = reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(scratch) + acc_bytes);
+    p.status = nullptr;  // the status word lives in allocated host memory; this path reports no timeouts
+
+    const bool mn_major = (x2_sn == 1);
+    CUtensorMap tw, tx;
+    int rc;
+    if (mn_major)
+        rc = make_tmap_2d(&tw, x2, 1, static_cast<uint64_t>(ep.N), static_cast<uint64_t>(K),
+                          static_cast<uint64_t>(x2_sk), 128, kSkBK, true);
+    else
+        rc = make_tmap_2d(&tw, x2, 1, static_cast<uint64_t>(K), static_cast<uint64_t>(ep.N),
+                          static_cast<uint64_t>(x2_sn), kSkBK, kSkTileN, true);
+    if (rc != QMM_OK) return rc;
+    rc = make_tmap_2d(&tx, x1, 1, static_cast<uint64_t>(K), static_cast<uint64_t>(ep.M),
+                      static_cast<uint64_t>(ld_x1), kSkBK, static_cast<uint32_t>(p.mpad), true);
+    if (rc != QMM_OK) return rc;
+
+    const int64_t total = static_cast<int64_t>(p.tiles_n) * p.kblocks;
+    const int grid = total < sm_count() ? static_cast<int>(total) : sm_count();
+    const size_t smem = 1024 + static_cast<size_t>(p.stages) * p.stage_bytes + sizeof(SkSmemTail);
+    auto kern = mn_major ? w8a8_streamk_kernel<OutT, true> : w8a8_streamk_kernel<OutT, false>;
+    QMM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(kSkSmemBudget)));
+    kern<<<grid, kSkThreads, smem, stream>>>(tw, tx, p);
+    QMM_CUDA_OK(cudaGetLastError());
+    return QMM_OK;
+}
+
+}  // namespace
+
+int validate_quant_matmul(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
+                          const float *scale, int64_t scale_len, const void *bias, int bias_dtype, void *out,
+                          int out_dtype, int64_t ld_out, int64_t M, int64_t N, int64_t K);
+
+}  // namespace qmm
+
+extern "C" int qmm_quant_matmul_decode_noalloc(const int8_t *x1, int64_t ld_x1, const int8_t *x2,
+                                               int64_t x2_stride_k, int64_t x2_stride_n, const float *scale,
+                                               int64_t scale_len, const float *pertoken_scale, const void *bias,
+                                               int bias_dtype, void *out, int out_dtype, int64_t ld_out, int64_t M,
+                                               int64_t N, int64_t K, void *stream) {
+    using namespace qmm;
+    int rc = validate_quant_matmul(x1, ld_x1, x2, x2_stride_k, x2_stride_n, scale, scale_len, bias, bias_dtype, out,
+                                   out_dtype, ld_out, M, N, K);
+    if (rc != QMM_OK) return rc;
+    if (M == 0 || N == 0) return QMM_OK;
+    if (!(M >= 1 && M <= 128 && K >= 1))
+        return fail(QMM_ERR_UNSUPPORTED, "qmm_quant_matmul_decode_noalloc: needs 1 <= M <= 128 and K >= 1, got M=" +
+                                             std::to_string(M) + " K=" + std::to_string(K));
+    const size_t need = streamk_workspace_bytes(M, N, K);
+    if (need > static_cast<size_t>(QMM_NOALLOC_SCRATCH_BYTES))
+        return fail(QMM_ERR_WORKSPACE, "qmm_quant_matmul_decode_noalloc: M=" + std::to_string(M) + ", N=" +
+                                           std::to_string(N) + " needs " + std::to_string(need) +
+                                           " bytes of scratch, the built-in buffer holds " +
+                                           std::to_string(static_cast<size_t>(QMM_NOALLOC_SCRATCH_BYTES)) +
+                                           "; use qmm_quant_matmul with a caller-provided workspace");
+    const bool aligned = ((reinterpret_cast<uintptr_t>(x1) & 15) == 0) && ((ld_x1 & 15) == 0) &&
+                         ((reinterpret_cast<uintptr_t>(x2) & 15) == 0) &&
+                         ((x2_stride_n == 1) ? ((x2_stride_k & 15) == 0) : ((x2_stride_n & 15) == 0));
+    if (!aligned)
+        return fail(QMM_ERR_UNSUPPORTED,
+                    "qmm_quant_matmul_decode_noalloc: operands need 16-byte aligned addresses and row pitches");
+    void *scratch = nullptr;
+    rc = noalloc_scratch_address(&scratch);
+    if (rc != QMM_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // The array keeps whatever the previous call left (zeros, unless that call was
+    // cut short): the partial sums and counters of this problem start from zero.
+    QMM_CUDA_OK(cudaMemsetAsync(scratch, 0, need, s));
+    EpilogueParams ep;
+    ep.scale = scale;
+    ep.pertoken_scale = (out_dtype == QMM_DTYPE_I32) ? nullptr : pertoken_scale;
+    ep.bias = bias;
+    ep.bias_dtype = bias ? bias_dtype : QMM_DTYPE_NONE;
+    ep.scale_is_scalar = (scale_len == 1 && N != 1) ? 1 : 0;
+    ep.out = out;
+    ep.ld_out = ld_out;
+    ep.M = M;
+    ep.N = N;
+    switch (out_dtype) {
+        case QMM_DTYPE_BF16:
+            return launch_streamk_noalloc_t<__nv_bfloat16>(x1, ld_x1, x2, x2_stride_k, x2_stride_n, ep, K, scratch, s);
+        case QMM_DTYPE_F16:
+            return launch_streamk_noalloc_t<__half>(x1, ld_x1, x2, x2_stride_k, x2_stride_n, ep, K, scratch, s);
+        default:
+            return launch_streamk_noalloc_t<int32_t>(x1, ld_x1, x2, x2_stride_k, x2_stride_n, ep, K, scratch, s);
+    }
+}

@@ -116,6 +116,35 @@ QMM_API int qmm_quant_matmul(const int8_t *x1, int64_t ld_x1, const int8_t *x2, 
                              void *workspace, size_t workspace_bytes, void *stream);
 
 /*
+ * Decode-shape W8A8 matmul that allocates nothing.  It has no counterpart in
+ * the reference: it exists for hosts that may not call cudaMalloc (or any
+ * allocator) once they are running — a server whose device memory was split up
+ * at start-up, a plugin bound by a no-allocation-after-init contract, a
+ * latency-critical thread that must stay off allocator locks.  Where
+ * qmm_quant_matmul takes its split-K scratch from the caller, this entry point
+ * uses a QMM_NOALLOC_SCRATCH_BYTES array that is part of the library image
+ * (each GPU that loads the library holds it until the process exits).
+ * Arguments and results are those of qmm_quant_matmul; the result is
+ * bit-identical to qmm_quant_matmul with QMM_ALGO_TCGEN05_STREAMK.
+ *   - 1 <= M <= 128, and ceil(N/128) * (round_up(M,16) * 512 + 4) + 252 bytes
+ *     must fit the array (e.g. M=128 up to N=32640, M=16 up to N=262016);
+ *     larger problems are refused with QMM_ERR_WORKSPACE.
+ *   - operands need 16-byte aligned addresses and row pitches.
+ *   - the first call on a device looks up the array's device address
+ *     (cudaGetSymbolAddress); make that first call before any stream capture.
+ *   - all calls on a device share the one array: calls that may overlap on the
+ *     GPU (different streams without ordering) race on it; keep them ordered.
+ *   - bounded device-side waits that give up are not reported by
+ *     qmm_device_status on this path.
+ */
+#define QMM_NOALLOC_SCRATCH_BYTES (16u << 20)
+QMM_API int qmm_quant_matmul_decode_noalloc(const int8_t *x1, int64_t ld_x1, const int8_t *x2,
+                                            int64_t x2_stride_k, int64_t x2_stride_n, const float *scale,
+                                            int64_t scale_len, const float *pertoken_scale, const void *bias,
+                                            int bias_dtype, void *out, int out_dtype, int64_t ld_out, int64_t M,
+                                            int64_t N, int64_t K, void *stream);
+
+/*
  * W4A16 matmul (torch op `npu_weight_quant_batchmatmul`; host conventions as
  * above plus the bias handling of
  * op_plugin/ops/base_ops/aclops/LinearKernelNpu.cpp:29-45).
