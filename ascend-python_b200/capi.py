@@ -24,7 +24,8 @@ UNIQUE_ID_BYTES = 128
 # every symbol include/qmm_b200.h declares
 EXPORTED_SYMBOLS = (
     "qmm_last_error", "qmm_version", "qmm_device_status", "qmm_dynamic_quant",
-    "qmm_quant_matmul_workspace_size", "qmm_quant_matmul", "qmm_weight_quant_batchmatmul",
+    "qmm_quant_matmul_workspace_size", "qmm_quant_matmul", "qmm_weight_quant_batchmatmul_workspace_size",
+    "qmm_weight_quant_batchmatmul",
     "qmm_comm_unique_id", "qmm_comm_init_rank", "qmm_comm_register", "qmm_comm_info", "qmm_comm_destroy",
     "qmm_mm_all_reduce", "qmm_quant_matmul_decode_noalloc",
 )
@@ -81,9 +82,13 @@ def lib() -> ctypes.CDLL:
                                                       c.c_void_p, c.c_int, c.c_int64, c.c_int64, c.c_int64,
                                                       c.c_int64, c.c_void_p]
         L.qmm_quant_matmul_decode_noalloc.restype = c.c_int
+        L.qmm_weight_quant_batchmatmul_workspace_size.argtypes = [c.c_int64, c.c_int64, c.c_int64, c.c_int64,
+                                                                  c.POINTER(c.c_size_t)]
+        L.qmm_weight_quant_batchmatmul_workspace_size.restype = c.c_int
         L.qmm_weight_quant_batchmatmul.argtypes = [c.c_void_p, c.c_int, c.c_int64, c.c_void_p, c.c_int64, c.c_void_p,
                                                    c.c_void_p, c.c_int64, c.c_void_p, c.c_void_p, c.c_int64,
-                                                   c.c_int64, c.c_int64, c.c_int64, c.c_void_p]
+                                                   c.c_int64, c.c_int64, c.c_int64, c.c_void_p, c.c_size_t,
+                                                   c.c_void_p]
         L.qmm_comm_unique_id.argtypes = [c.c_void_p]
         L.qmm_comm_init_rank.argtypes = [c.c_char_p, c.c_void_p, c.c_int, c.c_int]
         L.qmm_comm_register.argtypes = [c.c_char_p, c.c_void_p, c.c_int, c.c_int]
@@ -151,11 +156,12 @@ def quant_matmul_workspace_size(M: int, N: int, K: int, algo: int = ALGO_AUTO) -
 _workspaces = {}
 
 
-def get_workspace(device, nbytes: int) -> torch.Tensor | None:
-    """Zero-initialised scratch, cached per (device, stream); grown by reallocation."""
+def get_workspace(device, nbytes: int, kind: str = "w8a8") -> torch.Tensor | None:
+    """Zero-initialised scratch, cached per (kernel family, device, stream); grown by reallocation.
+    The families do not share a buffer: each relies on what it left behind itself."""
     if nbytes == 0:
         return None
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    key = (kind, device.index, torch.cuda.current_stream(device).cuda_stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
         ws = torch.zeros(nbytes, dtype=torch.uint8, device=device)
@@ -193,8 +199,10 @@ def quant_matmul(x1, x2, scale, pertoken_scale=None, bias=None, output_dtype=tor
     return out
 
 
-def weight_quant_batchmatmul(x, weight, antiquant_scale, antiquant_offset=None, bias=None, group_size=0):
-    """x [M,K] bf16/f16; weight int32 [K, N/8]; scale/offset [K/group, N]."""
+def weight_quant_batchmatmul(x, weight, antiquant_scale, antiquant_offset=None, bias=None, group_size=0,
+                             use_workspace=True):
+    """x [M,K] bf16/f16; weight int32 [K, N/8]; scale/offset [K/group, N].
+    use_workspace=False withholds the scratch, which selects the CUDA-core kernel."""
     assert x.is_cuda and weight.dtype == torch.int32
     M, K = x.shape
     N = weight.shape[1] * 8
@@ -202,10 +210,15 @@ def weight_quant_batchmatmul(x, weight, antiquant_scale, antiquant_offset=None, 
     x = x.contiguous()
     weight = weight.contiguous()
     out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    n = ctypes.c_size_t(0)
+    check(lib().qmm_weight_quant_batchmatmul_workspace_size(M, N, K, group, ctypes.byref(n)),
+          "qmm_weight_quant_batchmatmul_workspace_size")
+    ws_bytes = int(n.value) if use_workspace else 0
+    ws = get_workspace(x.device, ws_bytes, kind="w4a16")
     with torch.cuda.device(x.device):
         check(lib().qmm_weight_quant_batchmatmul(
             _ptr(x), dtype_code(x.dtype), K, _ptr(weight), weight.shape[1], _ptr(antiquant_scale.contiguous()),
             _ptr(None if antiquant_offset is None else antiquant_offset.contiguous()), group,
-            _ptr(None if bias is None else bias.contiguous()), _ptr(out), N, M, N, K, _stream()),
+            _ptr(None if bias is None else bias.contiguous()), _ptr(out), N, M, N, K, _ptr(ws), ws_bytes, _stream()),
             "qmm_weight_quant_batchmatmul")
     return out

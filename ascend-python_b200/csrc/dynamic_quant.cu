@@ -11,7 +11,7 @@
 //   q     = rint(x / scale)       IEEE fp32 division, round half to even
 // The division x / scale is evaluated as x * (1/scale) when that provably
 // rounds to the same integer, and by a true division when the product lands
-// within 1e-3 of a rounding tie (the two quotients differ by < 3e-5).
+// within 1e-4 of a rounding tie (product and quotient differ by < 2.3e-5).
 #include "qmm_common.cuh"
 
 namespace qmm {
@@ -68,6 +68,26 @@ __device__ __forceinline__ int quant_one(float x, const RowQuant &rq) {
     return max(-128, min(127, q));
 }
 
+// absmax of the eight 16-bit floats of a 128-bit vector, packed two at a time
+template <typename T>
+__device__ __forceinline__ float absmax8(const uint4 &v);
+template <>
+__device__ __forceinline__ float absmax8<__nv_bfloat16>(const uint4 &v) {
+    const uint32_t w[4] = {v.x & 0x7fff7fffu, v.y & 0x7fff7fffu, v.z & 0x7fff7fffu, v.w & 0x7fff7fffu};
+    __nv_bfloat162 m = __hmax2(__hmax2(*reinterpret_cast<const __nv_bfloat162 *>(&w[0]),
+                                       *reinterpret_cast<const __nv_bfloat162 *>(&w[1])),
+                               __hmax2(*reinterpret_cast<const __nv_bfloat162 *>(&w[2]),
+                                       *reinterpret_cast<const __nv_bfloat162 *>(&w[3])));
+    return fmaxf(__low2float(m), __high2float(m));
+}
+template <>
+__device__ __forceinline__ float absmax8<__half>(const uint4 &v) {
+    const uint32_t w[4] = {v.x & 0x7fff7fffu, v.y & 0x7fff7fffu, v.z & 0x7fff7fffu, v.w & 0x7fff7fffu};
+    __half2 m = __hmax2(__hmax2(*reinterpret_cast<const __half2 *>(&w[0]), *reinterpret_cast<const __half2 *>(&w[1])),
+                        __hmax2(*reinterpret_cast<const __half2 *>(&w[2]), *reinterpret_cast<const __half2 *>(&w[3])));
+    return fmaxf(__low2float(m), __high2float(m));
+}
+
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
@@ -97,12 +117,7 @@ dynamic_quant_vec_kernel(const T *__restrict__ x, int64_t rows, int cols, int64_
             v[i] = idx < nvec ? __ldg(src + idx) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            float f[8];
-            unpack8<T>(v[i], f);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
-        }
+        for (int i = 0; i < VPT; ++i) amax = fmaxf(amax, absmax8<T>(v[i]));
     }
     amax = warp_max(amax);
     if (tpr > 32) {
@@ -118,6 +133,7 @@ dynamic_quant_vec_kernel(const T *__restrict__ x, int64_t rows, int cols, int64_
     if (!row_ok) return;
     const RowQuant rq = make_row_quant(amax);
     if (t == 0) scale[row] = rq.scale;
+    const bool fast = !rq.exact_only && rq.scale != 0.0f;
 
     uint2 *dst = reinterpret_cast<uint2 *>(q + row * ld_q);
 #pragma unroll
@@ -127,10 +143,37 @@ dynamic_quant_vec_kernel(const T *__restrict__ x, int64_t rows, int cols, int64_
             float f[8];
             unpack8<T>(v[i], f);
             uint32_t lo = 0, hi = 0;
+            if (fast) {
+                // main path: four FMA-pipe operations per element, one max for the tie test
+                constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23: adding it rounds to an integer, ties to even
+                float r[8];
+                float dmax = 0.0f;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                lo |= (static_cast<uint32_t>(quant_one(f[j], rq)) & 0xffu) << (8 * j);
-                hi |= (static_cast<uint32_t>(quant_one(f[4 + j], rq)) & 0xffu) << (8 * j);
+                for (int j = 0; j < 8; ++j) {
+                    const float t = f[j] * rq.inv;
+                    r[j] = t + kMagic;
+                    dmax = fmaxf(dmax, fabsf(t - (r[j] - kMagic)));
+                }
+                if (dmax > 0.4999f) {
+                    // some product lies within 1e-4 of a rounding tie: let the exact quotient decide there
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float t = f[j] * rq.inv;
+                        if (fabsf(t - (r[j] - kMagic)) > 0.4999f) r[j] = rintf(__fdiv_rn(f[j], rq.scale)) + kMagic;
+                    }
+                }
+                uint32_t b[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) b[j] = __float_as_uint(r[j]);
+                // the int8 results are the low bytes of the biased floats: gather (b0..b3) and (b4..b7)
+                lo = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+                hi = __byte_perm(__byte_perm(b[4], b[5], 0x0040), __byte_perm(b[6], b[7], 0x0040), 0x5410);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    lo |= (static_cast<uint32_t>(quant_one(f[j], rq)) & 0xffu) << (8 * j);
+                    hi |= (static_cast<uint32_t>(quant_one(f[4 + j], rq)) & 0xffu) << (8 * j);
+                }
             }
             dst[idx] = make_uint2(lo, hi);
         }

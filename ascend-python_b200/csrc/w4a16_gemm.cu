@@ -5,13 +5,25 @@
 namespace qmm {
 // Implemented in w4a16_tc.cu: tcgen05 kernel for 16-byte aligned operands.
 bool w4a16_tc_supported(const W4Params &p, int x_dtype);
-int launch_w4a16_tc(const W4Params &p, int x_dtype, cudaStream_t stream);
+size_t w4a16_tc_workspace_bytes(int64_t M, int64_t N, int64_t K, int64_t group);
+int launch_w4a16_tc(const W4Params &p, int x_dtype, void *workspace, cudaStream_t stream);
 }  // namespace qmm
+
+extern "C" int qmm_weight_quant_batchmatmul_workspace_size(int64_t M, int64_t N, int64_t K, int64_t group,
+                                                           size_t *bytes) {
+    using namespace qmm;
+    QMM_REQUIRE(bytes != nullptr, "qmm_weight_quant_batchmatmul_workspace_size: bytes is NULL");
+    QMM_REQUIRE(M >= 0 && N >= 0 && K >= 0 && group >= 0,
+                "qmm_weight_quant_batchmatmul_workspace_size: negative argument");
+    *bytes = w4a16_tc_workspace_bytes(M, N, K, group > 0 ? group : K);
+    return QMM_OK;
+}
 
 extern "C" int qmm_weight_quant_batchmatmul(const void *x, int x_dtype, int64_t ld_x, const int32_t *weight,
                                             int64_t ld_w, const void *antiquant_scale, const void *antiquant_offset,
                                             int64_t group, const void *bias, void *out, int64_t ld_out, int64_t M,
-                                            int64_t N, int64_t K, void *stream) {
+                                            int64_t N, int64_t K, void *workspace, size_t workspace_bytes,
+                                            void *stream) {
     using namespace qmm;
     QMM_REQUIRE(M >= 0 && N >= 0 && K >= 0, "qmm_weight_quant_batchmatmul: negative dimension");
     QMM_REQUIRE(x_dtype == QMM_DTYPE_BF16 || x_dtype == QMM_DTYPE_F16,
@@ -44,7 +56,11 @@ extern "C" int qmm_weight_quant_batchmatmul(const void *x, int x_dtype, int64_t 
     p.N = N;
     p.K = K;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (K > 0 && w4a16_tc_supported(p, x_dtype)) return launch_w4a16_tc(p, x_dtype, s);
+    // tensor-core kernel when the operands meet TMA's 16-byte rules and scratch was provided
+    if (K > 0 && w4a16_tc_supported(p, x_dtype) && workspace != nullptr &&
+        (reinterpret_cast<uintptr_t>(workspace) & 255) == 0 &&
+        workspace_bytes >= w4a16_tc_workspace_bytes(M, N, K, p.group))
+        return launch_w4a16_tc(p, x_dtype, workspace, s);
     if (x_dtype == QMM_DTYPE_BF16) return launch_w4a16_simt<__nv_bfloat16>(p, s);
     return launch_w4a16_simt<__half>(p, s);
 }

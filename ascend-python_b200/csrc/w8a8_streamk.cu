@@ -21,12 +21,16 @@ namespace qmm {
 
 namespace {
 
-constexpr int kSkTileN = 128;  // output columns per tile = MMA M
+constexpr int kSkTileN = 128;  // output columns per MMA = MMA M
+constexpr int kSkHalves = 2;   // MMAs side by side per work unit: a unit is 256 columns wide, so that a
+                               // weight row contributes 256 contiguous bytes and the activation tile
+                               // is fetched once per two MMAs
+constexpr int kSkUnitN = kSkTileN * kSkHalves;
 constexpr int kSkBK = 128;     // k elements per stage
-constexpr int kSkABytes = kSkTileN * kSkBK;
+constexpr int kSkABytes = kSkUnitN * kSkBK;
 constexpr int kSkMaxStages = 8;
 constexpr int kSkThreads = 192;
-constexpr uint32_t kSkTmemCols = 256;  // two accumulators of up to 128 columns
+constexpr uint32_t kSkTmemCols = 512;  // two buffers x two accumulators of up to 128 columns
 constexpr size_t kSkSmemBudget = 200 * 1024;
 
 struct SkSmemTail {
@@ -38,6 +42,7 @@ struct SkSmemTail {
     uint32_t abort_flag;
     uint32_t is_last;
     uint32_t epi_abort;
+    float pertoken[128];  // per-token scales of the (at most 128) rows, staged once per CTA
 };
 
 struct SkParams {
@@ -46,10 +51,10 @@ struct SkParams {
     int mpad;         // M rounded up to a multiple of 16
     int stages;
     int stage_bytes;  // kSkABytes + mpad * kSkBK
-    int tiles_n;
+    int tiles_n;          // 256-column work units along N
     int kblocks;
-    int32_t *ws_acc;      // [tiles_n][mpad][128] int32, zero between calls
-    uint32_t *ws_count;   // [tiles_n], zero between calls
+    int32_t *ws_acc;      // [ceil(N/128)][mpad][128] int32, zero between calls
+    uint32_t *ws_count;   // one per work unit, zero between calls
     uint32_t *status;
 };
 
@@ -112,10 +117,13 @@ w8a8_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                 const uint32_t sa = smem_base + stage * p.stage_bytes;
                 const uint32_t sb = sa + kSkABytes;
                 mbar_expect_tx(full, static_cast<uint32_t>(p.stage_bytes));
-                if (A_MN_MAJOR)
-                    tma_load_2d(sa, &tmap_w, tile * kSkTileN, kb * kSkBK, full);  // [128 k-rows][128 n-bytes]
-                else
-                    tma_load_2d(sa, &tmap_w, kb * kSkBK, tile * kSkTileN, full);  // [128 n-rows][128 k-bytes]
+                if (A_MN_MAJOR) {
+                    // two [128 k-rows][128 n-bytes] boxes, one per 128-column half
+                    tma_load_2d(sa, &tmap_w, tile * kSkUnitN, kb * kSkBK, full);
+                    tma_load_2d(sa + kSkABytes / 2, &tmap_w, tile * kSkUnitN + kSkTileN, kb * kSkBK, full);
+                } else {
+                    tma_load_2d(sa, &tmap_w, kb * kSkBK, tile * kSkUnitN, full);  // [256 n-rows][128 k-bytes]
+                }
                 tma_load_2d(sb, &tmap_x, kb * kSkBK, 0, full);                    // [mpad m-rows][128 k-bytes]
             }
             __syncwarp();
@@ -141,7 +149,7 @@ w8a8_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             ok = mbar_wait(smem_u32(&tail->tmem_empty[buf]), buf_phase ^ 1, abort_flag, 0x12);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t d_tmem = tmem_base + buf * 128;
+            const uint32_t d_tmem = tmem_base + buf * 256;
             bool first = true;
             for (; u < seg_end; ++u) {
                 ok = mbar_wait(smem_u32(&tail->full[stage]), phase, abort_flag, 0x13);
@@ -152,10 +160,14 @@ w8a8_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                     const uint32_t sb = sa + kSkABytes;
 #pragma unroll
                     for (int k = 0; k < kSkBK / 32; ++k) {
-                        const uint64_t adesc = A_MN_MAJOR ? make_smem_desc_sw128(sa + k * 4096, 1024, 1024)
-                                                          : make_smem_desc_sw128(sa + k * 32, 16, 1024);
                         const uint64_t bdesc = make_smem_desc_sw128(sb + k * 32, 16, 1024);
-                        mma_i8_ss(d_tmem, adesc, bdesc, idesc, (first && k == 0) ? 0u : 1u);
+#pragma unroll
+                        for (int h = 0; h < kSkHalves; ++h) {
+                            const uint32_t sah = sa + h * (kSkABytes / 2);
+                            const uint64_t adesc = A_MN_MAJOR ? make_smem_desc_sw128(sah + k * 4096, 1024, 1024)
+                                                              : make_smem_desc_sw128(sah + k * 32, 16, 1024);
+                            mma_i8_ss(d_tmem + h * kSkTileN, adesc, bdesc, idesc, (first && k == 0) ? 0u : 1u);
+                        }
                     }
                     tc_commit(smem_u32(&tail->empty[stage]));
                 }
@@ -177,6 +189,9 @@ w8a8_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         const bool leader = (threadIdx.x == 64);
         const EpilogueParams &ep = p.ep;
         const int M = static_cast<int>(ep.M);
+        // every thread needs every row's per-token scale: one coalesced fetch per CTA, broadcasts afterwards
+        if (ep.pertoken_scale != nullptr && row < M) tail->pertoken[row] = __ldg(ep.pertoken_scale + row);
+        epi_bar_sync();
         int seg = 0;
         bool ok = true;
         int64_t u = u_begin;
@@ -197,9 +212,11 @@ w8a8_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             if (*reinterpret_cast<volatile uint32_t *>(&tail->epi_abort) != 0) break;
             tc_fence_after();
 
-            const int64_t n = static_cast<int64_t>(tile) * kSkTileN + row;
+#pragma unroll 1
+            for (int h = 0; h < kSkHalves; ++h) {
+            const int64_t n = static_cast<int64_t>(tile) * kSkUnitN + h * kSkTileN + row;
             const bool n_ok = n < ep.N;
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * 128;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * 256 + h * kSkTileN;
 
             // per-column constants of the dequantization
             float sc = 0.0f, bi = 0.0f;
@@ -222,12 +239,12 @@ w8a8_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                 if constexpr (sizeof(OutT) == 4) {
                     *reinterpret_cast<int32_t *>(o) = acc + bi32;
                 } else {
-                    const float pt = has_pt ? __ldg(ep.pertoken_scale + m) : 1.0f;
+                    const float pt = has_pt ? tail->pertoken[m] : 1.0f;
                     *o = from_float<OutT>(dequant_one(acc, sc, pt, has_pt, bi, has_bias));
                 }
             };
 
-            int32_t *ws = p.ws_acc + (static_cast<int64_t>(tile) * p.mpad) * kSkTileN + row;
+            int32_t *ws = p.ws_acc + (static_cast<int64_t>(tile * kSkHalves + h) * p.mpad) * kSkTileN + row;
             for (int c = 0; c < p.mpad; c += 16) {
                 uint32_t acc[16];
                 tmem_ld_32x16(taddr + c, acc);
@@ -245,6 +262,7 @@ w8a8_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                     }
                 }
             }
+            }  // halves
             // accumulator buffer can be reused by the MMA warp
             tc_fence_before();
             __syncwarp();
@@ -261,12 +279,23 @@ w8a8_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                 }
                 epi_bar_sync();
                 if (tail->is_last) {
-                    if (n_ok) {
-                        for (int m = 0; m < M; ++m) {
-                            int32_t *a = ws + static_cast<int64_t>(m) * kSkTileN;
-                            const int32_t v = __ldcg(a);
-                            __stcg(a, 0);
-                            finish(m, v);
+                    for (int h = 0; h < kSkHalves; ++h) {
+                        const int64_t n = static_cast<int64_t>(tile) * kSkUnitN + h * kSkTileN + row;
+                        if (n < ep.N) {
+                            int32_t *ws = p.ws_acc + (static_cast<int64_t>(tile * kSkHalves + h) * p.mpad) * kSkTileN + row;
+                            // sixteen independent loads at a time: one L2 round trip per batch, not per row
+                            for (int m0 = 0; m0 < M; m0 += 16) {
+                                int32_t v[16];
+#pragma unroll
+                                for (int j = 0; j < 16; ++j)
+                                    v[j] = (m0 + j < M) ? __ldcg(ws + static_cast<int64_t>(m0 + j) * kSkTileN) : 0;
+#pragma unroll
+                                for (int j = 0; j < 16; ++j)
+                                    if (m0 + j < M) __stcg(ws + static_cast<int64_t>(m0 + j) * kSkTileN, 0);
+#pragma unroll
+                                for (int j = 0; j < 16; ++j)
+                                    if (m0 + j < M) epilogue_one<OutT>(ep, m0 + j, n, v[j]);
+                            }
                         }
                     }
                     if (leader) p.ws_count[tile] = 0;
@@ -315,9 +344,9 @@ static int launch_streamk_t(const int8_t *x1, int64_t ld_x1, const int8_t *x2, i
     p.stage_bytes = kSkABytes + p.mpad * kSkBK;
     int stages = static_cast<int>((kSkSmemBudget - 1024 - sizeof(SkSmemTail)) / p.stage_bytes);
     p.stages = stages > kSkMaxStages ? kSkMaxStages : stages;
-    p.tiles_n = static_cast<int>((ep.N + kSkTileN - 1) / kSkTileN);
+    p.tiles_n = static_cast<int>((ep.N + kSkUnitN - 1) / kSkUnitN);
     p.kblocks = static_cast<int>((K + kSkBK - 1) / kSkBK);
-    const size_t acc_bytes = static_cast<size_t>(p.tiles_n) * p.mpad * kSkTileN * sizeof(int32_t);
+    const size_t acc_bytes = static_cast<size_t>((ep.N + kSkTileN - 1) / kSkTileN) * p.mpad * kSkTileN * sizeof(int32_t);
     p.ws_acc = static_cast<int32_t *>(workspace);
     p.ws_count = reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(workspace) + acc_bytes);
     p.status = device_status_word();
@@ -330,7 +359,7 @@ static int launch_streamk_t(const int8_t *x1, int64_t ld_x1, const int8_t *x2, i
                           static_cast<uint64_t>(x2_sk), 128, kSkBK, true);
     else
         rc = make_tmap_2d(&tw, x2, 1, static_cast<uint64_t>(K), static_cast<uint64_t>(ep.N),
-                          static_cast<uint64_t>(x2_sn), kSkBK, kSkTileN, true);
+                          static_cast<uint64_t>(x2_sn), kSkBK, kSkUnitN, true);
     if (rc != QMM_OK) return rc;
     rc = make_tmap_2d(&tx, x1, 1, static_cast<uint64_t>(K), static_cast<uint64_t>(ep.M),
                       static_cast<uint64_t>(ld_x1), kSkBK, static_cast<uint32_t>(p.mpad), true);
@@ -422,9 +451,9 @@ int launch_streamk_noalloc_t(const int8_t *x1, int64_t ld_x1, const int8_t *x2, 
     p.stage_bytes = kSkABytes + p.mpad * kSkBK;
     int stages = static_cast<int>((kSkSmemBudget - 1024 - sizeof(SkSmemTail)) / p.stage_bytes);
     p.stages = stages > kSkMaxStages ? kSkMaxStages : stages;
-    p.tiles_n = static_cast<int>((ep.N + kSkTileN - 1) / kSkTileN);
+    p.tiles_n = static_cast<int>((ep.N + kSkUnitN - 1) / kSkUnitN);
     p.kblocks = static_cast<int>((K + kSkBK - 1) / kSkBK);
-    const size_t acc_bytes = static_cast<size_t>(p.tiles_n) * p.mpad * kSkTileN * sizeof(int32_t);
+    const size_t acc_bytes = static_cast<size_t>((ep.N + kSkTileN - 1) / kSkTileN) * p.mpad * kSkTileN * sizeof(int32_t);
     p.ws_acc = static_cast<int32_t *>(scratch);
     p.ws_count = reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(scratch) + acc_bytes);
     p.status = nullptr;  // the status word lives in allocated host memory; this path reports no timeouts
@@ -437,7 +466,7 @@ int launch_streamk_noalloc_t(const int8_t *x1, int64_t ld_x1, const int8_t *x2, 
                           static_cast<uint64_t>(x2_sk), 128, kSkBK, true);
     else
         rc = make_tmap_2d(&tw, x2, 1, static_cast<uint64_t>(K), static_cast<uint64_t>(ep.N),
-                          static_cast<uint64_t>(x2_sn), kSkBK, kSkTileN, true);
+                          static_cast<uint64_t>(x2_sn), kSkBK, kSkUnitN, true);
     if (rc != QMM_OK) return rc;
     rc = make_tmap_2d(&tx, x1, 1, static_cast<uint64_t>(K), static_cast<uint64_t>(ep.M),
                       static_cast<uint64_t>(ld_x1), kSkBK, static_cast<uint32_t>(p.mpad), true);

@@ -73,10 +73,15 @@ at::Tensor npu_weight_quant_batchmatmul(const at::Tensor &x, const at::Tensor &w
     at::Tensor sc = antiquant_scale.contiguous();
     at::Tensor oc = offset_real.defined() ? offset_real.contiguous() : offset_real;
     at::Tensor bc = bias_real.defined() ? bias_real.contiguous() : bias_real;
+    size_t workspace_size = 0;
+    EXEC_QMM_CMD(qmm_weight_quant_batchmatmul_workspace_size, M, N, K, group, &workspace_size);
+    at::Tensor workspace = op_plugin_utils::qmm_workspace(xc, workspace_size, /*family=*/1);
     EXEC_QMM_CMD(qmm_weight_quant_batchmatmul, xc.const_data_ptr(), op_plugin_utils::qmm_dtype(xc.scalar_type()),
                  std::max<int64_t>(K, 1), static_cast<const int32_t *>(wc.const_data_ptr()),
                  std::max<int64_t>(N / 8, 1), sc.const_data_ptr(), op_plugin_utils::opt_ptr(oc), group,
-                 op_plugin_utils::opt_ptr(bc), result.data_ptr(), N, M, N, K, op_plugin_utils::current_stream(xc));
+                 op_plugin_utils::opt_ptr(bc), result.data_ptr(), N, M, N, K,
+                 workspace.defined() ? workspace.data_ptr() : nullptr, workspace_size,
+                 op_plugin_utils::current_stream(xc));
     return result;
 }
 

@@ -2,6 +2,7 @@
 
 #include <map>
 #include <mutex>
+#include <tuple>
 #include <utility>
 
 namespace op_plugin_utils {
@@ -27,16 +28,16 @@ void *current_stream(const at::Tensor &like)
     return static_cast<void *>(at::cuda::getCurrentCUDAStream(like.device().index()).stream());
 }
 
-at::Tensor qmm_workspace(const at::Tensor &like, size_t bytes)
+at::Tensor qmm_workspace(const at::Tensor &like, size_t bytes, int family)
 {
     static std::mutex mutex;
     // leaked on purpose: tensors must not be destroyed after the CUDA runtime at process exit
-    static auto &cache = *new std::map<std::pair<int, void *>, at::Tensor>();
+    static auto &cache = *new std::map<std::tuple<int, int, void *>, at::Tensor>();
     if (bytes == 0) {
         return at::Tensor();
     }
     std::lock_guard<std::mutex> lock(mutex);
-    auto key = std::make_pair(static_cast<int>(like.device().index()), current_stream(like));
+    auto key = std::make_tuple(family, static_cast<int>(like.device().index()), current_stream(like));
     auto it = cache.find(key);
     if (it == cache.end() || static_cast<size_t>(it->second.numel()) < bytes) {
         at::Tensor ws = at::zeros({static_cast<int64_t>(bytes)}, like.options().dtype(at::kByte));

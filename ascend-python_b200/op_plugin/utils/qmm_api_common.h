@@ -35,7 +35,8 @@ void *current_stream(const at::Tensor &like);
 // Zero-initialised scratch of at least `bytes`, cached per (device, stream) and
 // grown on demand.  The kernels that use it leave it zeroed, so one buffer is
 // reused by consecutive launches of the same stream (stream order serializes them).
-at::Tensor qmm_workspace(const at::Tensor &like, size_t bytes);
+// `family` separates kernel families: each relies on the state it left in its own buffer.
+at::Tensor qmm_workspace(const at::Tensor &like, size_t bytes, int family = 0);
 
 // data pointer of an optional tensor (nullptr when absent)
 inline const void *opt_ptr(const at::Tensor &t) { return t.defined() ? t.const_data_ptr() : nullptr; }

@@ -156,12 +156,17 @@ QMM_API int qmm_quant_matmul_decode_noalloc(const int8_t *x1, int64_t ld_x1, con
  * [K/group, N] of x_dtype (offset may be NULL = 0).  group must divide K and
  * be a multiple of 32; group == K gives per-channel quantization.
  * out: [M,N] of x_dtype, row stride ld_out.
+ * workspace: scratch of at least qmm_weight_quant_batchmatmul_workspace_size bytes, 256-byte
+ * aligned, zero-filled before its first use only (the kernel leaves it reusable).  Without it
+ * (NULL), or with operands that break the 16-byte rules of TMA, a CUDA-core kernel runs.
  */
+QMM_API int qmm_weight_quant_batchmatmul_workspace_size(int64_t M, int64_t N, int64_t K, int64_t group,
+                                                        size_t *bytes);
 QMM_API int qmm_weight_quant_batchmatmul(const void *x, int x_dtype, int64_t ld_x, const int32_t *weight,
                                          int64_t ld_w, const void *antiquant_scale,
                                          const void *antiquant_offset, int64_t group, const void *bias,
                                          void *out, int64_t ld_out, int64_t M, int64_t N, int64_t K,
-                                         void *stream);
+                                         void *workspace, size_t workspace_bytes, void *stream);
 
 /*
  * Communicator registry.  The reference passes a communicator NAME into its

@@ -38,7 +38,7 @@ def test_validation_needs_no_gpu(capi):
     rc = lib.qmm_quant_matmul(None, 8, None, 8, 1, None, 0, None, None, -1, None, 7, 8, 4, 8, 8, 0, None, 0, None)
     assert rc == 1 and b"output dtype" in lib.qmm_last_error()
     rc = lib.qmm_weight_quant_batchmatmul(None, capi.DTYPE_BF16, 8, None, 1, None, None, 128, None, None, 12, 1, 12,
-                                          8, None)
+                                          8, None, 0, None)
     assert rc == 1 and b"multiple of 8" in lib.qmm_last_error()
     nr, rk = ctypes.c_int(0), ctypes.c_int(0)
     rc = lib.qmm_comm_info(b"no-such-comm", ctypes.byref(nr), ctypes.byref(rk))

@@ -13,7 +13,7 @@ ULP_TOL = 1  # bf16/f16 units in the last place
 
 
 def _algos(capi, M):
-    return [capi.ALGO_TILE, capi.ALGO_SIMT] + ([capi.ALGO_STREAMK] if 1 <= M <= 128 else [])
+    return [capi.ALGO_TILE, capi.ALGO_PAIR, capi.ALGO_SIMT] + ([capi.ALGO_STREAMK] if 1 <= M <= 128 else [])
 
 
 def _make(oracle, M, K, N, seed, dtype=torch.bfloat16):
