@@ -9,8 +9,8 @@
 // (op_plugin/utils/op_api_common.h:80-123), so that the process uses the one
 // libnccl its framework already loaded.
 //
-// Overlap: M is cut into chunks; chunk c's matmul runs on the caller's stream,
-// an event hands the finished rows to the communication stream, whose
+// Overlap (comm_turn > 1): M is cut into chunks; chunk c's matmul runs on the caller's
+// stream, an event hands the finished rows to the communication stream, whose
 // in-place ncclAllReduce of chunk c runs while chunk c+1 is being multiplied.
 // The matmul leaves a few SMs free while a collective may be in flight.
 #include <dlfcn.h>
@@ -39,6 +39,7 @@ struct NcclApi {
     void *handle = nullptr;
     ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
     ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommInitRankConfig)(ncclComm_t *, int, ncclUniqueId, int, ncclConfig_t *) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
     ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t,
@@ -71,6 +72,9 @@ NcclApi &nccl() {
         };
         api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(sym("ncclGetUniqueId"));
         api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(sym("ncclCommInitRank"));
+        // optional: absent from very old NCCL builds, then the communicator is created without a CTA cap
+        api.CommInitRankConfig =
+            reinterpret_cast<decltype(api.CommInitRankConfig)>(dlsym(api.handle, "ncclCommInitRankConfig"));
         api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(sym("ncclCommDestroy"));
         api.CommAbort = reinterpret_cast<decltype(api.CommAbort)>(sym("ncclCommAbort"));
         api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(sym("ncclAllReduce"));
@@ -94,6 +98,19 @@ int nccl_ready() {
     } while (0)
 
 constexpr int kMaxChunks = 16;
+
+// CTAs a collective of ours may use, and therefore SMs the matmul leaves idle while a collective can
+// be in flight: the matmul's persistent CTAs fill the shared memory of the SMs they run on, so a
+// collective CTA only ever lands on an SM the matmul left free; a collective that wanted more CTAs
+// than that would finish only after the matmul chunk beside it, and nothing would overlap.
+int comm_ctas() {
+    static int n = [] {
+        const char *e = getenv("QMM_COMM_MAX_CTAS");
+        int v = e ? atoi(e) : 32;
+        return v < 1 ? 1 : (v > 64 ? 64 : v);
+    }();
+    return n;
+}
 
 struct Comm {
     ncclComm_t comm = nullptr;
@@ -169,7 +186,13 @@ extern "C" int qmm_comm_init_rank(const char *name, const void *id, int nranks, 
     c.owned = true;
     ncclUniqueId uid;
     memcpy(&uid, id, sizeof(uid));
-    QMM_NCCL_OK(nccl().CommInitRank(&c.comm, nranks, uid, rank));
+    if (nccl().CommInitRankConfig != nullptr) {
+        ncclConfig_t config = NCCL_CONFIG_INITIALIZER;
+        config.maxCTAs = comm_ctas();
+        QMM_NCCL_OK(nccl().CommInitRankConfig(&c.comm, nranks, uid, rank, &config));
+    } else {
+        QMM_NCCL_OK(nccl().CommInitRank(&c.comm, nranks, uid, rank));
+    }
     rc = create_stream_events(c);
     if (rc != QMM_OK) {
         release(c, true);
@@ -266,9 +289,11 @@ extern "C" int qmm_mm_all_reduce(const int8_t *x1, int64_t ld_x1, const int8_t *
     QMM_REQUIRE(dev == c.device, "qmm_mm_all_reduce: communicator belongs to another device");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
 
-    // number of M chunks: each at least 512 rows, so that a chunk still fills the machine
-    int chunks = comm_turn > 0 ? static_cast<int>(comm_turn < kMaxChunks ? comm_turn : kMaxChunks)
-                               : (c.nranks == 1 ? 1 : static_cast<int>(M / 1024));
+    // Number of M chunks.  Measured on 2, 4 and 8 B200s (M=4096, N=8192): every extra ncclAllReduce call
+    // costs tens of microseconds and a collective confined to the SMs the matmul leaves free runs far
+    // below link speed, so cutting M into chunks lost more than the overlap won back (2 GPUs: 423 us
+    // unchunked, 486 us in 4 chunks).  The default is therefore one chunk; comm_turn > 0 asks for more.
+    int chunks = comm_turn > 0 ? static_cast<int>(comm_turn < kMaxChunks ? comm_turn : kMaxChunks) : 1;
     if (chunks < 1) chunks = 1;
     if (chunks > kMaxChunks) chunks = kMaxChunks;
     int64_t rows_per = (M + chunks - 1) / chunks;
@@ -290,7 +315,7 @@ extern "C" int qmm_mm_all_reduce(const int8_t *x1, int64_t ld_x1, const int8_t *
         ep.M = rows;
         ep.N = N;
         // leave SMs to a collective that may be running beside this chunk
-        set_sm_reserve((c.nranks > 1 && ci > 0) ? 16 : 0);
+        set_sm_reserve((c.nranks > 1 && ci > 0) ? comm_ctas() : 0);
         rc = quant_matmul_dispatch(x1 + m0 * ld_x1, ld_x1, x2, x2_stride_k, x2_stride_n, ep, out_dtype, K,
                                    K == 0 ? QMM_ALGO_SIMT : QMM_ALGO_AUTO, workspace, workspace_bytes, s);
         set_sm_reserve(0);
