@@ -312,6 +312,81 @@ __host__ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_
     return d;
 }
 
+// The same descriptor split into its two 32-bit halves.  The high half is a constant of the
+// kernel; the low half is (address >> 4) | (lbo >> 4) << 16, so stepping through a tile is one
+// 32-bit add.  (Shared-memory addresses are below 256 KiB: address >> 4 fits the 14-bit field.)
+__host__ __device__ constexpr uint32_t smem_desc_hi_sw128(uint32_t sbo_bytes) {
+    return ((sbo_bytes >> 4) & 0x3fffu) | (1u << 14) | (2u << 29);
+}
+__host__ __device__ constexpr uint32_t smem_desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+    return (smem_addr >> 4) | (((lbo_bytes >> 4) & 0x3fffu) << 16);
+}
+__device__ __forceinline__ uint64_t desc64(uint32_t lo, uint32_t hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+    return d;
+}
+
+// Issue forms for a whole, converged warp: every lane executes the call with the same operands and
+// elect.sync lets one lane (always the same one) issue.  Operands stay warp-uniform, which keeps the
+// issue loop short: a single thread can otherwise spend ~200 cycles per MMA on scalar bookkeeping,
+// more than a 128x256x32 MMA takes to execute.
+__device__ __forceinline__ void mma_i8_ss_warp(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_f16_ss_warp(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_i8_ss_pair_warp(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                    uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "@e tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_commit_warp(uint32_t bar) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+        "}\n" ::"r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair_warp(uint32_t bar, uint16_t cta_mask) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "@e tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n\t"
+        "}\n" ::"r"(bar),
+        "h"(cta_mask)
+        : "memory");
+}
+
 // Instruction descriptor for kind::i8 / kind::f16 (dense, no negate, no saturate).
 //   c_format: 1 = f32, 2 = s32;  ab_format: i8 -> 1 (signed); f16 kind -> 0 f16, 1 bf16
 //   a_mn_major / b_mn_major: 0 = K-major operand, 1 = MN-major operand

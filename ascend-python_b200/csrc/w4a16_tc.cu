@@ -4,22 +4,28 @@
 //
 // The inner sums run on tcgen05 (kind::f16, fp32 accumulator in TMEM) over the RAW 4-bit
 // integers, which are exact in bf16/f16; scale and offset are applied once per group to the
-// accumulator, not once per weight.  Per 64-row k-block a CTA
-//   1. receives the packed words [64 k][128 n / 8] (4 KiB) and the activations [M16][64 k] by TMA,
+// accumulator, not once per weight.
+//
+// A work unit is 512 output columns x one quantization group.  512 columns are 256 contiguous
+// bytes of a packed weight row: narrower strips (the 64 bytes of a 128-column tile) leave HBM
+// with one short burst per DRAM page.  Per 16 k-rows a CTA
+//   1. receives the packed words [16 k][512 n / 8] (4 KiB) by TMA (the activations [M16][64 k]
+//      arrive once per 64 k-rows through their own ring),
 //   2. turns every packed word into eight 16-bit floats with four logic operations
 //      (nibble | exponent bits = BIAS + w; for bf16 BIAS = 136 stays in the operand and is folded
-//      into the offset term, for f16 the constant 1032 is subtracted on the spot) and stores them as one 16-byte vector into the MMA's
-//      MN-major, 128-byte-swizzled A tile,
-//   3. issues four 128 x M16 x 16 MMAs: weights are the M operand (TMEM lane = output column,
-//      so row stores are coalesced), tokens padded to a multiple of 16 are the N operand.
+//      into the offset term, for f16 the constant 1032 is subtracted on the spot) and stores
+//      them as one 16-byte vector into the MN-major, 128-byte-swizzled A tiles,
+//   3. issues four 128 x M16 x 16 MMAs, one per 128-column sub-tile: weights are the M operand
+//      (TMEM lane = output column, so row stores are coalesced), tokens padded to a multiple of
+//      16 are the N operand.
 // Within a 16-byte vector the columns appear in the order 0,4,1,5,2,6,3,7 (what the logic
 // operations produce without a shuffle); the epilogue maps lanes back to columns.
 //
-// Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2-5
-// dequantization (one warp per k-block, four k-blocks in flight), warps 6-9 per-group scaling and epilogue.  Work is cut stream-K style into
-// equal contiguous ranges of (column tile, group) units; a tile shared by several CTAs is
-// summed from per-CTA slots in slot order by the last arriver, so results do not depend on
-// arrival order.
+// Warp roles (832 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2-9
+// dequantization (two warps per 16-row step, four steps in flight), warps 10-25 per-group scaling
+// and epilogue (four warps per sub-tile).  Work is cut stream-K style into equal contiguous
+// ranges of (column unit, group); a unit shared by several CTAs is summed from per-CTA slots in
+// slot order by the last arriver, so results do not depend on arrival order.
 #include "qmm_common.cuh"
 #include "w4a16_simt.cuh"
 
@@ -27,23 +33,31 @@ namespace qmm {
 
 namespace {
 
-constexpr int kWTileN = 128;
-constexpr int kWBK = 64;                    // k rows per stage: one 128-byte swizzle row of 16-bit activations
-constexpr int kWPackedBytes = kWBK * (kWTileN / 8) * 4;  // 4 KiB of packed words per stage
-constexpr int kWABytes = kWBK * kWTileN * 2;             // 16 KiB dequantized A tile
+constexpr int kWTileN = 128;                 // columns per MMA (its M dimension)
+constexpr int kWSub = 4;                     // MMAs side by side
+constexpr int kWUnitN = kWTileN * kWSub;     // 512 columns per work unit
+constexpr int kWBK = 64;                     // k rows per activation tile: one 128-byte swizzle row
+constexpr int kWStepK = 16;                  // k rows per weight stage = one MMA
+constexpr int kWPackedBytes = kWStepK * (kWUnitN / 8) * 4;  // 4 KiB of packed words per step
+constexpr int kWABytes = kWStepK * kWUnitN * 2;             // 16 KiB of dequantized A per step
+constexpr int kWASubBytes = kWABytes / kWSub;               // 4 KiB per sub-tile
 constexpr int kWABufs = 4;
-constexpr int kWMaxStages = 16;
-constexpr int kWThreads = 320;
+constexpr int kWStages = 16;                 // packed-weight stages (64 KiB in flight)
+constexpr int kWXStages = 4;                 // activation tiles
+constexpr int kWDeqWarps = 8;               // two warps per 16-row step
+constexpr int kWThreads = 64 + kWDeqWarps * 32 + 16 * 32;  // 832
+constexpr int kWEpiWarps = 16;
 constexpr int kWMaxM = 64;
-constexpr int kWAccBufs = 4;                 // group accumulators in flight
-constexpr uint32_t kWTmemCols = 256;        // four accumulators of up to 64 columns
-constexpr size_t kWSmemBudget = 216 * 1024;
-constexpr size_t kWXsSmemBytes = 16 * 1024;
-constexpr size_t kWCounterBytes = 64 * 1024;  // tile counters: up to 16384 column tiles  // shared copy of the group sums of x
+constexpr int kWAccBufs = 2;                 // group accumulators in flight
+constexpr uint32_t kWTmemCols = 512;        // 2 buffers x 4 sub-tiles x up to 64 columns
+constexpr size_t kWXsSmemBytes = 16 * 1024;  // shared copy of the group sums of x
+constexpr size_t kWCounterBytes = 64 * 1024;  // unit counters: a fixed area at the start of the scratch
 
 struct WSmemTail {
-    uint64_t full[kWMaxStages];
-    uint64_t empty[kWMaxStages];
+    uint64_t full[kWStages];
+    uint64_t empty[kWStages];
+    uint64_t x_full[kWXStages];
+    uint64_t x_empty[kWXStages];
     uint64_t a_full[kWABufs];
     uint64_t a_empty[kWABufs];
     uint64_t tmem_full[kWAccBufs];
@@ -57,20 +71,19 @@ struct WSmemTail {
 struct WTcParams {
     W4Params w;
     int mpad;            // M rounded up to 16
-    int stages;
-    int stage_bytes;     // kWPackedBytes + mpad * 128
-    int tiles_n;
+    int x_bytes;         // mpad * 128: one activation tile
+    int units_n;         // 512-column units along N
     int ngroups;
-    int kb_per_group;    // group / 64
+    int steps_per_group; // group / 16
     int max_slots;
     int xs_in_smem;      // the group sums fit the shared-memory area reserved for them
     const float *xsum;   // [ngroups][64]: sum over the group's k of x[m,k]
-    float *slots;        // [tiles_n][max_slots][mpad][128]
-    uint32_t *counters;  // [tiles_n], zero between calls
+    float *slots;        // [units_n][max_slots][4][mpad][128]
+    uint32_t *counters;  // [units_n], zero between calls
     uint32_t *status;
 };
 
-__device__ __forceinline__ void wepi_bar_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+__device__ __forceinline__ void wepi_bar_sync() { asm volatile("bar.sync 2, 512;" ::: "memory"); }
 
 // CTA whose contiguous unit range [total*b/G, total*(b+1)/G) contains unit u
 __device__ __forceinline__ int cta_of_unit(int64_t u, int64_t total, int64_t G) {
@@ -127,7 +140,7 @@ namespace qmm {
 namespace {
 
 struct WTcPlan {
-    int mpad, tiles_n, ngroups, kb_per_group, grid, max_slots;
+    int mpad, units_n, ngroups, steps_per_group, grid, max_slots;
     size_t counters_bytes, xsum_bytes, slots_bytes;
 };
 
@@ -135,10 +148,10 @@ WTcPlan make_plan(int64_t M, int64_t N, int64_t K, int64_t group) {
     WTcPlan pl;
     const int64_t m = M < kWMaxM ? M : kWMaxM;
     pl.mpad = static_cast<int>((m + 15) / 16 * 16);
-    pl.tiles_n = static_cast<int>((N + kWTileN - 1) / kWTileN);
+    pl.units_n = static_cast<int>((N + kWUnitN - 1) / kWUnitN);
     pl.ngroups = static_cast<int>(K / group);
-    pl.kb_per_group = static_cast<int>(group / kWBK);
-    const int64_t total = static_cast<int64_t>(pl.tiles_n) * pl.ngroups;
+    pl.steps_per_group = static_cast<int>(group / kWStepK);
+    const int64_t total = static_cast<int64_t>(pl.units_n) * pl.ngroups;
     pl.grid = static_cast<int>(total < sm_count() ? total : sm_count());
     const int64_t upc = total / pl.grid;  // units per CTA, rounded down (>= 1)
     pl.max_slots = static_cast<int>((pl.ngroups + upc - 1) / upc + 1);
@@ -146,7 +159,7 @@ WTcPlan make_plan(int64_t M, int64_t N, int64_t K, int64_t group) {
     // start of the scratch, so that no other shape's sums ever land where a later call expects zeros.
     pl.counters_bytes = kWCounterBytes;
     pl.xsum_bytes = static_cast<size_t>(pl.ngroups) * kWMaxM * sizeof(float);
-    pl.slots_bytes = static_cast<size_t>(pl.tiles_n) * pl.max_slots * pl.mpad * kWTileN * sizeof(float);
+    pl.slots_bytes = static_cast<size_t>(pl.units_n) * pl.max_slots * kWSub * pl.mpad * kWTileN * sizeof(float);
     return pl;
 }
 
@@ -156,14 +169,11 @@ int launch_w4a16_tc_t(const W4Params &w, void *workspace, cudaStream_t stream) {
     WTcParams p;
     p.w = w;
     p.mpad = pl.mpad;
-    p.stage_bytes = kWPackedBytes + pl.mpad * 128;
-    int stages = static_cast<int>((kWSmemBudget - 1024 - kWABufs * kWABytes - sizeof(WSmemTail) - kWXsSmemBytes) /
-                                  p.stage_bytes);
+    p.x_bytes = pl.mpad * 128;
     p.xs_in_smem = (static_cast<size_t>(pl.ngroups) * pl.mpad * sizeof(float) <= kWXsSmemBytes) ? 1 : 0;
-    p.stages = stages > kWMaxStages ? kWMaxStages : stages;
-    p.tiles_n = pl.tiles_n;
+    p.units_n = pl.units_n;
     p.ngroups = pl.ngroups;
-    p.kb_per_group = pl.kb_per_group;
+    p.steps_per_group = pl.steps_per_group;
     p.max_slots = pl.max_slots;
     uint8_t *ws = static_cast<uint8_t *>(workspace);
     p.counters = reinterpret_cast<uint32_t *>(ws);
@@ -174,7 +184,7 @@ int launch_w4a16_tc_t(const W4Params &w, void *workspace, cudaStream_t stream) {
 
     CUtensorMap tw, tx;
     int rc = make_tmap_2d(&tw, w.w, 4, static_cast<uint64_t>(w.N / 8), static_cast<uint64_t>(w.K),
-                          static_cast<uint64_t>(w.ld_w), kWTileN / 8, kWBK, false);
+                          static_cast<uint64_t>(w.ld_w), kWUnitN / 8, kWStepK, false);
     if (rc != QMM_OK) return rc;
     rc = make_tmap_2d(&tx, w.x, 2, static_cast<uint64_t>(w.K), static_cast<uint64_t>(w.M),
                       static_cast<uint64_t>(w.ld_x), kWBK, static_cast<uint32_t>(pl.mpad), true);
@@ -184,11 +194,10 @@ int launch_w4a16_tc_t(const W4Params &w, void *workspace, cudaStream_t stream) {
         static_cast<const T *>(w.x), w.ld_x, static_cast<int>(w.M), w.group, xsum);
     QMM_CUDA_OK(cudaGetLastError());
 
-    const size_t smem = 1024 + kWABufs * kWABytes + static_cast<size_t>(p.stages) * p.stage_bytes +
-                        sizeof(WSmemTail) + kWXsSmemBytes;
-    auto kern = w4a16_tc_kernel<T>;
-    QMM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     static_cast<int>(kWSmemBudget)));
+    const size_t smem = 1024 + kWABufs * kWABytes + kWStages * kWPackedBytes +
+                        static_cast<size_t>(kWXStages) * p.x_bytes + sizeof(WSmemTail) + kWXsSmemBytes;
+    auto kern = pl.mpad <= 32 ? w4a16_tc_kernel<T, 32> : w4a16_tc_kernel<T, 64>;
+    QMM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     kern<<<pl.grid, kWThreads, smem, stream>>>(tw, tx, p);
     QMM_CUDA_OK(cudaGetLastError());
     return QMM_OK;
@@ -202,7 +211,7 @@ bool w4a16_tc_supported(const W4Params &p, int x_dtype) {
     if (p.group % kWBK != 0) return false;
     if ((reinterpret_cast<uintptr_t>(p.x) & 15) || (p.ld_x & 7)) return false;
     if ((reinterpret_cast<uintptr_t>(p.w) & 15) || (p.ld_w & 3)) return false;
-    if ((p.N + kWTileN - 1) / kWTileN > static_cast<int64_t>(kWCounterBytes / 4)) return false;
+    if ((p.N + kWUnitN - 1) / kWUnitN > static_cast<int64_t>(kWCounterBytes / 4)) return false;
     return p.K < (1ll << 31) && p.N < (1ll << 31);
 }
 

@@ -2,40 +2,47 @@
 namespace qmm {
 namespace {
 
-template <typename T>
+// ACC_M: accumulator registers per epilogue thread (32 or 64 token rows)
+template <typename T, int ACC_M>
 __global__ void __launch_bounds__(kWThreads, 1)
 w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                 WTcParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
-    // [A tiles][stages: packed words + activations][barriers]
-    const uint32_t a_base = smem_base;
-    const uint32_t st_base = smem_base + kWABufs * kWABytes;
-    WSmemTail *tail = reinterpret_cast<WSmemTail *>(smem_aligned + kWABufs * kWABytes + p.stages * p.stage_bytes);
+    // [A tiles][activation tiles][packed-weight stages][barriers][group sums of x]
+    constexpr uint32_t kAOff = 0;
+    constexpr uint32_t kXOff = kWABufs * kWABytes;
+    const uint32_t kWOff = kXOff + kWXStages * p.x_bytes;
+    WSmemTail *tail = reinterpret_cast<WSmemTail *>(smem_aligned + kWOff + kWStages * kWPackedBytes);
     float *xs_smem = reinterpret_cast<float *>(tail + 1);  // [ngroups][mpad] when p.xs_in_smem
     volatile uint32_t *abort_flag = &tail->abort_flag;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int64_t total = static_cast<int64_t>(p.tiles_n) * p.ngroups;
+    const int64_t total = static_cast<int64_t>(p.units_n) * p.ngroups;
     const int64_t G = gridDim.x;
     const int64_t u_begin = total * blockIdx.x / G;
     const int64_t u_end = total * (blockIdx.x + 1) / G;
-    const int kbg = p.kb_per_group;
+    const int spg = p.steps_per_group;  // 16-row steps per group (a multiple of 4)
+    const int64_t nsteps = (u_end - u_begin) * spg;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < p.stages; ++s) {
+        for (int s = 0; s < kWStages; ++s) {
             mbar_init(smem_u32(&tail->full[s]), 1);
-            mbar_init(smem_u32(&tail->empty[s]), 1);
+            mbar_init(smem_u32(&tail->empty[s]), 2);
+        }
+        for (int s = 0; s < kWXStages; ++s) {
+            mbar_init(smem_u32(&tail->x_full[s]), 1);
+            mbar_init(smem_u32(&tail->x_empty[s]), 1);
         }
         for (int a = 0; a < kWABufs; ++a) {
-            mbar_init(smem_u32(&tail->a_full[a]), 1);
+            mbar_init(smem_u32(&tail->a_full[a]), 2);
             mbar_init(smem_u32(&tail->a_empty[a]), 1);
         }
         for (int b = 0; b < kWAccBufs; ++b) {
             mbar_init(smem_u32(&tail->tmem_full[b]), 1);
-            mbar_init(smem_u32(&tail->tmem_empty[b]), 4);
+            mbar_init(smem_u32(&tail->tmem_empty[b]), kWEpiWarps);
         }
         tail->abort_flag = 0;
         tail->is_last = 0;
@@ -57,112 +64,151 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
-        uint32_t stage = 0, phase = 0;
-        bool ok = true;
-        for (int64_t u = u_begin; u < u_end && ok; ++u) {
-            const int tile = static_cast<int>(u / p.ngroups);
-            const int g = static_cast<int>(u - static_cast<int64_t>(tile) * p.ngroups);
-            for (int kb = 0; kb < kbg; ++kb) {
-                ok = mbar_wait(smem_u32(&tail->empty[stage]), phase ^ 1, abort_flag, 0x31);
-                if (!ok) break;
+        // step i of this CTA belongs to unit u_begin + i / spg and covers rows k0 .. k0+15 of it;
+        // all counters advance incrementally (no divisions in the loop)
+        int unit = static_cast<int>(u_begin / p.ngroups);
+        int g = static_cast<int>(u_begin - static_cast<int64_t>(unit) * p.ngroups);
+        int s_in_g = 0;
+        uint32_t st = 0, ph = 0, xs = 0, xph = 0;
+        const uint32_t full0 = smem_u32(&tail->full[0]), empty0 = smem_u32(&tail->empty[0]);
+        const uint32_t xfull0 = smem_u32(&tail->x_full[0]), xempty0 = smem_u32(&tail->x_empty[0]);
+        for (int64_t i = 0; i < nsteps; ++i) {
+            const int k0 = (g * spg + s_in_g) * kWStepK;
+            if ((s_in_g & 3) == 0) {
+                // a fresh 64-row activation tile every fourth step
+                if (!mbar_wait(xempty0 + xs * 8, xph ^ 1, abort_flag, 0x30)) break;
                 if (lane == 0) {
-                    const uint32_t full = smem_u32(&tail->full[stage]);
-                    const uint32_t sw = st_base + stage * p.stage_bytes;
-                    const uint32_t sx = sw + kWPackedBytes;
-                    const int k0 = (g * kbg + kb) * kWBK;
-                    mbar_expect_tx(full, static_cast<uint32_t>(p.stage_bytes));
-                    tma_load_2d(sw, &tmap_w, tile * (kWTileN / 8), k0, full);  // [64 k][16 words]
-                    tma_load_2d(sx, &tmap_x, k0, 0, full);                      // [mpad m][64 k]
+                    mbar_expect_tx(xfull0 + xs * 8, static_cast<uint32_t>(p.x_bytes));
+                    tma_load_2d(smem_base + kXOff + xs * p.x_bytes, &tmap_x, k0, 0, xfull0 + xs * 8);  // [mpad m][64 k]
                 }
-                __syncwarp();
-                if (++stage == static_cast<uint32_t>(p.stages)) {
-                    stage = 0;
-                    phase ^= 1;
+                if (++xs == kWXStages) {
+                    xs = 0;
+                    xph ^= 1;
+                }
+            }
+            if (!mbar_wait(empty0 + st * 8, ph ^ 1, abort_flag, 0x31)) break;
+            if (lane == 0) {
+                mbar_expect_tx(full0 + st * 8, kWPackedBytes);
+                tma_load_2d(smem_base + kWOff + st * kWPackedBytes, &tmap_w, unit * (kWUnitN / 8), k0, full0 + st * 8);
+            }
+            __syncwarp();
+            if (++st == kWStages) {
+                st = 0;
+                ph ^= 1;
+            }
+            if (++s_in_g == spg) {
+                s_in_g = 0;
+                if (++g == p.ngroups) {
+                    g = 0;
+                    ++unit;
                 }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
+        // The whole warp runs the loop with warp-uniform operands; elect.sync picks the issuing lane.
         const uint32_t idesc = make_idesc(/*c=f32*/ 1, W4Magic<T>::kFmt, W4Magic<T>::kFmt, /*a MN-major*/ 1,
                                           /*b K-major*/ 0, kWTileN, static_cast<uint32_t>(p.mpad));
-        uint32_t stage = 0, phase = 0, abuf = 0, aphase = 0;
-        int local = 0;
+        constexpr uint32_t kDescHi = smem_desc_hi_sw128(1024);
+        // A sub-tile: MN-major; two 64-column halves 2 KiB apart (leading offset), 8-row groups 1 KiB apart
+        const uint32_t a_lo0 = smem_desc_lo(smem_base + kAOff, kWASubBytes / 2);
+        // B: K-major activations; 16 k elements = 32 bytes (+2) per step within the 64-k tile
+        const uint32_t b_lo0 = smem_desc_lo(smem_base + kXOff, 16);
+        const uint32_t x_step = static_cast<uint32_t>(p.x_bytes) >> 4;
+        const uint32_t afull0 = smem_u32(&tail->a_full[0]), aempty0 = smem_u32(&tail->a_empty[0]);
+        const uint32_t xfull0 = smem_u32(&tail->x_full[0]), xempty0 = smem_u32(&tail->x_empty[0]);
         bool ok = true;
-        for (int64_t u = u_begin; u < u_end && ok; ++u, ++local) {
-            const uint32_t pb = local % kWAccBufs;
-            const uint32_t pb_phase = (local / kWAccBufs) & 1;
+        uint32_t ab = 0, aph = 0, xs = 0, xph = 0, pb = 0, pb_phase = 0;
+        const int64_t nunits = u_end - u_begin;
+        for (int64_t local = 0; local < nunits && ok; ++local) {
             ok = mbar_wait(smem_u32(&tail->tmem_empty[pb]), pb_phase ^ 1, abort_flag, 0x32);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t d_tmem = tmem_base + pb * kWMaxM;
-            for (int kb = 0; kb < kbg; ++kb) {
-                // the activations arrive with the stage, the dequantized weights with the A tile
-                ok = mbar_wait(smem_u32(&tail->full[stage]), phase, abort_flag, 0x33) &&
-                     mbar_wait(smem_u32(&tail->a_full[abuf]), aphase, abort_flag, 0x34);
+            const uint32_t d_tmem = tmem_base + pb * (kWSub * kWMaxM);
+            uint32_t accumulate = 0;
+            for (int s = 0; s < spg; ++s) {
+                ok = mbar_wait(afull0 + ab * 8, aph, abort_flag, 0x34);
+                if (ok && (s & 3) == 0) ok = mbar_wait(xfull0 + xs * 8, xph, abort_flag, 0x33);
                 if (!ok) break;
                 tc_fence_after();
-                if (lane == 0) {
-                    const uint32_t sa = a_base + abuf * kWABytes;
-                    const uint32_t sx = st_base + stage * p.stage_bytes + kWPackedBytes;
+                const uint64_t bdesc = desc64(b_lo0 + xs * x_step + 2 * (s & 3), kDescHi);
+                const uint32_t a_lo = a_lo0 + ab * (kWABytes >> 4);
 #pragma unroll
-                    for (int k = 0; k < kWBK / 16; ++k) {
-                        // A: MN-major; 64 columns (128 bytes) per row, 8-k-row groups 1024 bytes apart,
-                        // second 64-column half 8 KiB further; 16 k rows = 2048 bytes per MMA
-                        const uint64_t adesc = make_smem_desc_sw128(sa + k * 2048, kWABytes / 2, 1024);
-                        // B: K-major; 16 k elements = 32 bytes per MMA
-                        const uint64_t bdesc = make_smem_desc_sw128(sx + k * 32, 16, 1024);
-                        mma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                for (int t = 0; t < kWSub; ++t)
+                    mma_f16_ss_warp(d_tmem + t * kWMaxM, desc64(a_lo + t * (kWASubBytes >> 4), kDescHi), bdesc, idesc,
+                                    accumulate);
+                accumulate = 1;
+                tc_commit_warp(aempty0 + ab * 8);
+                if (++ab == kWABufs) {
+                    ab = 0;
+                    aph ^= 1;
+                }
+                if ((s & 3) == 3) {
+                    tc_commit_warp(xempty0 + xs * 8);
+                    if (++xs == kWXStages) {
+                        xs = 0;
+                        xph ^= 1;
                     }
-                    tc_commit(smem_u32(&tail->empty[stage]));
-                    tc_commit(smem_u32(&tail->a_empty[abuf]));
-                }
-                __syncwarp();
-                if (++stage == static_cast<uint32_t>(p.stages)) {
-                    stage = 0;
-                    phase ^= 1;
-                }
-                if (++abuf == kWABufs) {
-                    abuf = 0;
-                    aphase ^= 1;
                 }
             }
-            if (ok && lane == 0) tc_commit(smem_u32(&tail->tmem_full[pb]));
-            __syncwarp();
+            if (ok) tc_commit_warp(smem_u32(&tail->tmem_full[pb]));
+            if (++pb == kWAccBufs) {
+                pb = 0;
+                pb_phase ^= 1;
+            }
         }
-    } else if (warp < 6) {
+    } else if (warp < 2 + kWDeqWarps) {
         // ---------------- dequantization warps ----------------
-        // Warp w converts the k-blocks i = w, w+4, ... of this CTA into A buffer w, so four k-blocks
-        // are in flight and the fixed costs (barrier wake-up, proxy fence) are paid once per 8 KiB of
-        // packed words and warp.  Per step a warp reads two packed rows (lane -> word, conflict-free)
-        // and writes 32 vectors of 16 bytes (conflict-free under the 128-byte swizzle).
-        const int wq = warp - 2;
-        const int wd = lane & 15;      // packed word within the row: columns 8*wd .. 8*wd+7 of the tile
-        const int half = wd >> 3;      // which 64-column half of the tile
-        const int j = wd & 7;          // 16-byte chunk within the 128-byte row of that half
-        const int64_t kblocks = (u_end - u_begin) * kbg;
-        for (int64_t i = wq; i < kblocks; i += kWABufs) {
-            const uint32_t stage = static_cast<uint32_t>(i % p.stages);
-            const uint32_t phase = static_cast<uint32_t>((i / p.stages) & 1);
-            const uint32_t aphase = static_cast<uint32_t>((i / kWABufs) & 1);
-            if (!(mbar_wait(smem_u32(&tail->full[stage]), phase, abort_flag, 0x35) &&
-                  mbar_wait(smem_u32(&tail->a_empty[wq]), aphase ^ 1, abort_flag, 0x36)))
+        // Warps 2w and 2w+1 convert the steps i = w, w+4, ... of this CTA into A buffer w (eight rows
+        // each), so four steps are in flight and the fixed costs (barrier wake-up, proxy fence) are
+        // paid once per 2 KiB of packed words and warp.  Per iteration a warp reads 32 consecutive
+        // words (conflict-free) and writes 32 vectors of 16 bytes (conflict-free under the swizzle).
+        const int wq = (warp - 2) >> 1;   // A buffer / step residue
+        const int hr = (warp - 2) & 1;    // which eight k rows of the step
+        // lane-dependent parts of the destination address, for words 0..31 and 32..63 of a row
+        uint32_t base[2], j16[2];
+#pragma unroll
+        for (int par = 0; par < 2; ++par) {
+            const int wd = (par << 5) + lane;  // word within the row: columns 8*wd .. 8*wd+7
+            base[par] = (wd >> 4) * kWASubBytes + ((wd >> 3) & 1) * (kWASubBytes / 2) + hr * 1024;
+            j16[par] = (wd & 7) << 4;          // 16-byte chunk within the 128-byte row
+        }
+        static_assert(kWStages % kWABufs == 0, "a warp pair revisits the same stages every kWStages / kWABufs steps");
+        uint32_t st = wq, ph = 0, aph = 0;
+        for (int64_t i = wq; i < nsteps; i += kWABufs) {
+            if (!(mbar_wait(smem_u32(&tail->full[st]), ph, abort_flag, 0x35) &&
+                  mbar_wait(smem_u32(&tail->a_empty[wq]), aph ^ 1, abort_flag, 0x36)))
                 break;
-            const uint8_t *packed = smem_aligned + kWABufs * kWABytes + stage * p.stage_bytes + wd * 4;
-            uint8_t *dst_half = smem_aligned + wq * kWABytes + half * (kWABytes / 2);
-#pragma unroll 8
-            for (int it = 0; it < kWBK / 2; ++it) {
-                const int r = it * 2 + (lane >> 4);
-                const uint32_t u = *reinterpret_cast<const uint32_t *>(packed + r * 64) ^ 0x88888888u;
-                uint4 v;  // two's complement nibble -> offset binary -> BIAS + w in a 16-bit float
+            const uint32_t *packed =
+                reinterpret_cast<const uint32_t *>(smem_aligned + kWOff + st * kWPackedBytes) + hr * 512 + lane;
+            uint8_t *abuf = smem_aligned + kAOff + wq * kWABytes;
+            uint32_t words[16];
+#pragma unroll
+            for (int it = 0; it < 16; ++it) words[it] = packed[it * 32];
+            // the packed words are in registers: the stage can be refilled
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&tail->empty[st]));
+#pragma unroll
+            for (int it = 0; it < 16; ++it) {
+                const int r7 = it >> 1;      // k row within this warp's eight rows (= row & 7)
+                const int par = it & 1;
+                const uint32_t u = words[it] ^ 0x88888888u;  // two's complement nibble -> offset binary
+                uint4 v;                                     // -> BIAS + w in a 16-bit float
                 v.x = W4Magic<T>::finish((u & 0x000f000fu) | W4Magic<T>::kExp);          // columns 0 and 4
                 v.y = W4Magic<T>::finish(((u >> 4) & 0x000f000fu) | W4Magic<T>::kExp);   // columns 1 and 5
                 v.z = W4Magic<T>::finish(((u >> 8) & 0x000f000fu) | W4Magic<T>::kExp);   // columns 2 and 6
                 v.w = W4Magic<T>::finish(((u >> 12) & 0x000f000fu) | W4Magic<T>::kExp);  // columns 3 and 7
-                *reinterpret_cast<uint4 *>(dst_half + (r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4)) = v;
+                *reinterpret_cast<uint4 *>(abuf + base[par] + r7 * 128 + (j16[par] ^ (r7 << 4))) = v;
             }
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&tail->a_full[wq]));
+            aph ^= 1;
+            st += kWABufs;
+            if (st >= kWStages) {
+                st -= kWStages;
+                ph ^= 1;
+            }
         }
     } else {
 #include "w4a16_tc_epilogue.inl"

@@ -158,8 +158,18 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
+        // The whole warp runs the loop with warp-uniform operands; elect.sync picks the issuing lane.
         constexpr uint32_t idesc = make_idesc(/*c=s32*/ 2, /*a=s8*/ 1, /*b=s8*/ 1, /*a K-major*/ 0,
                                               B_MN_MAJOR ? 1u : 0u, kBM, kBN);
+        constexpr uint32_t kDescHi = smem_desc_hi_sw128(1024);  // 8-row groups are 1024 bytes apart
+        constexpr uint32_t kStageStep = kStageBytes >> 4;
+        // A: K-major, 32 bytes (+2) per K step.  B: MN-major (second 128-column half 16 KiB further)
+        // 32 k-rows = 4096 bytes (+256) per K step; K-major +2.
+        constexpr uint32_t kBStep = B_MN_MAJOR ? (4096u >> 4) : 2u;
+        const uint32_t a_lo0 = smem_desc_lo(smem_base, 16);
+        const uint32_t b_lo0 = smem_desc_lo(smem_base + kAStageBytes, B_MN_MAJOR ? kBStageBytes / 2 : 16);
+        const uint32_t full0 = smem_u32(&tail->full[0]);
+        const uint32_t empty0 = smem_u32(&tail->empty[0]);
         uint32_t stage = 0, phase = 0;
         int local = 0;
         bool ok = true;
@@ -170,37 +180,26 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (!ok) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + buf * kBN;
+            uint32_t accumulate = 0;
             for (int kb = 0; kb < num_kb; ++kb) {
-                ok = mbar_wait(smem_u32(&tail->full[stage]), phase, abort_flag, 3);
+                ok = mbar_wait(full0 + stage * 8, phase, abort_flag, 3);
                 if (!ok) break;
                 tc_fence_after();
-                if (lane == 0) {
-                    const uint32_t sa = smem_base + stage * kStageBytes;
-                    const uint32_t sb = sa + kAStageBytes;
+                const uint32_t a_lo = a_lo0 + stage * kStageStep;
+                const uint32_t b_lo = b_lo0 + stage * kStageStep;
 #pragma unroll
-                    for (int k = 0; k < kBK / 32; ++k) {
-                        // A: K-major, 128-byte swizzle; 8-row groups 1024 bytes apart; 32 bytes per K step
-                        const uint64_t adesc = make_smem_desc_sw128(sa + k * 32, 16, 1024);
-                        uint64_t bdesc;
-                        if (B_MN_MAJOR) {
-                            // B: MN-major; 128 n-bytes per row, 8 k-row groups 1024 bytes apart,
-                            // second 128-column half 16 KiB further; 32 k-rows (4096 bytes) per K step
-                            bdesc = make_smem_desc_sw128(sb + k * 4096, kBStageBytes / 2, 1024);
-                        } else {
-                            bdesc = make_smem_desc_sw128(sb + k * 32, 16, 1024);
-                        }
-                        mma_i8_ss(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-                    }
-                    tc_commit(smem_u32(&tail->empty[stage]));
+                for (int k = 0; k < kBK / 32; ++k) {
+                    mma_i8_ss_warp(d_tmem, desc64(a_lo + 2 * k, kDescHi), desc64(b_lo + kBStep * k, kDescHi), idesc,
+                                   accumulate);
+                    accumulate = 1;
                 }
-                __syncwarp();
+                tc_commit_warp(empty0 + stage * 8);
                 if (++stage == kStages) {
                     stage = 0;
                     phase ^= 1;
                 }
             }
-            if (ok && lane == 0) tc_commit(smem_u32(&tail->tmem_full[buf]));
-            __syncwarp();
+            if (ok) tc_commit_warp(smem_u32(&tail->tmem_full[buf]));
         }
     } else {
         // ---------------- epilogue warps ----------------
@@ -369,6 +368,18 @@ int launch_simt(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk
     return QMM_OK;
 }
 
+// Decode shapes (M <= 128): stream-K keeps every SM streaming weights whatever N is, but its split
+// tiles pay for the int32 scratch traffic, which grows with M.  Measured on B200 (K x N = 8192 x 28672
+// and 28672 x 8192): up to 16 tokens stream-K wins everywhere; beyond that the one-CTA tile kernel is
+// ahead as soon as its 128 x 256 tiles occupy most SMs (52 us against 65 us at M = 32, 54 us against
+// 117 us at M = 128 for N = 28672), and for narrow N from about 64 tokens on.
+bool prefer_streamk(int64_t M, int64_t N) {
+    if (M <= 16) return true;
+    const int64_t tiles = (N + kBN - 1) / kBN;
+    if (tiles * 10 >= static_cast<int64_t>(sm_count()) * 7) return false;
+    return M <= 64;
+}
+
 bool tma_compatible(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn) {
     if ((reinterpret_cast<uintptr_t>(x1) & 15) || (ld_x1 & 15)) return false;
     if (reinterpret_cast<uintptr_t>(x2) & 15) return false;
@@ -395,7 +406,7 @@ int quant_matmul_dispatch(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int
         if (!tma_ok)
             algo = QMM_ALGO_SIMT;
         else if (streamk_supported(ep.M, ep.N, K, x2_sn) && workspace != nullptr &&
-                 workspace_bytes >= streamk_workspace_bytes(ep.M, ep.N, K))
+                 workspace_bytes >= streamk_workspace_bytes(ep.M, ep.N, K) && prefer_streamk(ep.M, ep.N))
             algo = QMM_ALGO_TCGEN05_STREAMK;
         else if (ep.M > 128)
             algo = QMM_ALGO_TCGEN05_PAIR;  // a few percent ahead of the one-CTA kernel under the power cap

@@ -147,8 +147,17 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer (leader CTA only) ----------------
+        // The whole warp runs the loop with warp-uniform operands; elect.sync picks the issuing lane.
         if (leader) {
             constexpr uint32_t idesc = make_idesc(/*c=s32*/ 2, 1, 1, /*a K-major*/ 0, B_MN_MAJOR ? 1u : 0u, 2 * kPM, kPN);
+            constexpr uint32_t kDescHi = smem_desc_hi_sw128(1024);  // 8-row groups are 1024 bytes apart
+            constexpr uint32_t kStageStep = kPStageBytes >> 4;
+            // A: K-major, 32 bytes (+2) per K step.  B: MN-major 4096 bytes (+256) per K step, K-major +2.
+            constexpr uint32_t kBStep = B_MN_MAJOR ? (4096u >> 4) : 2u;
+            const uint32_t a_lo0 = smem_desc_lo(smem_base, 16);
+            const uint32_t b_lo0 = smem_desc_lo(smem_base + kPAStageBytes, B_MN_MAJOR ? 1024u : 16u);
+            const uint32_t full0 = smem_u32(&tail->full[0]);
+            const uint32_t empty0 = smem_u32(&tail->empty[0]);
             uint32_t stage = 0, phase = 0;
             int local = 0;
             bool ok = true;
@@ -159,30 +168,26 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * kPN;
+                uint32_t accumulate = 0;
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    ok = mbar_wait(smem_u32(&tail->full[stage]), phase, abort_flag, 0x23);
+                    ok = mbar_wait(full0 + stage * 8, phase, abort_flag, 0x23);
                     if (!ok) break;
                     tc_fence_after();
-                    if (lane == 0) {
-                        const uint32_t sa = smem_base + stage * kPStageBytes;
-                        const uint32_t sb = sa + kPAStageBytes;
+                    const uint32_t a_lo = a_lo0 + stage * kStageStep;
+                    const uint32_t b_lo = b_lo0 + stage * kStageStep;
 #pragma unroll
-                        for (int k = 0; k < kPK / 32; ++k) {
-                            const uint64_t adesc = make_smem_desc_sw128(sa + k * 32, 16, 1024);
-                            const uint64_t bdesc = B_MN_MAJOR ? make_smem_desc_sw128(sb + k * 4096, 1024, 1024)
-                                                              : make_smem_desc_sw128(sb + k * 32, 16, 1024);
-                            mma_i8_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-                        }
-                        tc_commit_pair(smem_u32(&tail->empty[stage]), 0x3);
+                    for (int k = 0; k < kPK / 32; ++k) {
+                        mma_i8_ss_pair_warp(d_tmem, desc64(a_lo + 2 * k, kDescHi), desc64(b_lo + kBStep * k, kDescHi),
+                                            idesc, accumulate);
+                        accumulate = 1;
                     }
-                    __syncwarp();
+                    tc_commit_pair_warp(empty0 + stage * 8, 0x3);
                     if (++stage == kPStages) {
                         stage = 0;
                         phase ^= 1;
                     }
                 }
-                if (ok && lane == 0) tc_commit_pair(smem_u32(&tail->tmem_full[buf]), 0x3);
-                __syncwarp();
+                if (ok) tc_commit_pair_warp(smem_u32(&tail->tmem_full[buf]), 0x3);
             }
         }
     } else {

@@ -108,12 +108,14 @@ w8a8_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         uint32_t stage = 0, phase = 0;
+        int tile = static_cast<int>(u_begin / p.kblocks);
+        int kb = static_cast<int>(u_begin - static_cast<int64_t>(tile) * p.kblocks);
+        const uint32_t full0 = smem_u32(&tail->full[0]);
+        const uint32_t empty0 = smem_u32(&tail->empty[0]);
         for (int64_t u = u_begin; u < u_end; ++u) {
-            const int tile = static_cast<int>(u / p.kblocks);
-            const int kb = static_cast<int>(u - static_cast<int64_t>(tile) * p.kblocks);
-            if (!mbar_wait(smem_u32(&tail->empty[stage]), phase ^ 1, abort_flag, 0x11)) break;
+            if (!mbar_wait(empty0 + stage * 8, phase ^ 1, abort_flag, 0x11)) break;
             if (lane == 0) {
-                const uint32_t full = smem_u32(&tail->full[stage]);
+                const uint32_t full = full0 + stage * 8;
                 const uint32_t sa = smem_base + stage * p.stage_bytes;
                 const uint32_t sb = sa + kSkABytes;
                 mbar_expect_tx(full, static_cast<uint32_t>(p.stage_bytes));
@@ -127,6 +129,10 @@ w8a8_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                 tma_load_2d(sb, &tmap_x, kb * kSkBK, 0, full);                    // [mpad m-rows][128 k-bytes]
             }
             __syncwarp();
+            if (++kb == p.kblocks) {
+                kb = 0;
+                ++tile;
+            }
             if (++stage == static_cast<uint32_t>(p.stages)) {
                 stage = 0;
                 phase ^= 1;
@@ -134,15 +140,25 @@ w8a8_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
+        // The whole warp runs the loop with warp-uniform operands; elect.sync picks the issuing lane.
+        // Descriptors advance by 32-bit adds on their low words (the issue loop is the critical path:
+        // with 16 tokens an MMA executes in a few tens of cycles).
         const uint32_t idesc = make_idesc(/*c=s32*/ 2, 1, 1, A_MN_MAJOR ? 1u : 0u, /*b K-major*/ 0, kSkTileN,
                                           static_cast<uint32_t>(p.mpad));
+        constexpr uint32_t kDescHi = smem_desc_hi_sw128(1024);
+        constexpr uint32_t kAStep = A_MN_MAJOR ? (4096u >> 4) : 2u;  // per 32-element K step
+        constexpr uint32_t kAHalf = (kSkABytes / 2) >> 4;
+        const uint32_t a_lo0 = smem_desc_lo(smem_base, A_MN_MAJOR ? 1024u : 16u);
+        const uint32_t b_lo0 = smem_desc_lo(smem_base + kSkABytes, 16);
+        const uint32_t stage_step = static_cast<uint32_t>(p.stage_bytes) >> 4;
+        const uint32_t full0 = smem_u32(&tail->full[0]);
+        const uint32_t empty0 = smem_u32(&tail->empty[0]);
         uint32_t stage = 0, phase = 0;
         int seg = 0;
         bool ok = true;
         int64_t u = u_begin;
+        int64_t tile_end = (u_begin / p.kblocks + 1) * static_cast<int64_t>(p.kblocks);
         while (u < u_end && ok) {
-            const int tile = static_cast<int>(u / p.kblocks);
-            const int64_t tile_end = static_cast<int64_t>(tile + 1) * p.kblocks;
             const int64_t seg_end = tile_end < u_end ? tile_end : u_end;
             const uint32_t buf = seg & 1;
             const uint32_t buf_phase = (seg >> 1) & 1;
@@ -150,36 +166,31 @@ w8a8_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             if (!ok) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + buf * 256;
-            bool first = true;
+            uint32_t accumulate = 0;
             for (; u < seg_end; ++u) {
-                ok = mbar_wait(smem_u32(&tail->full[stage]), phase, abort_flag, 0x13);
+                ok = mbar_wait(full0 + stage * 8, phase, abort_flag, 0x13);
                 if (!ok) break;
                 tc_fence_after();
-                if (lane == 0) {
-                    const uint32_t sa = smem_base + stage * p.stage_bytes;
-                    const uint32_t sb = sa + kSkABytes;
+                const uint32_t a_lo = a_lo0 + stage * stage_step;
+                const uint32_t b_lo = b_lo0 + stage * stage_step;
 #pragma unroll
-                    for (int k = 0; k < kSkBK / 32; ++k) {
-                        const uint64_t bdesc = make_smem_desc_sw128(sb + k * 32, 16, 1024);
+                for (int k = 0; k < kSkBK / 32; ++k) {
+                    const uint64_t bdesc = desc64(b_lo + 2 * k, kDescHi);
 #pragma unroll
-                        for (int h = 0; h < kSkHalves; ++h) {
-                            const uint32_t sah = sa + h * (kSkABytes / 2);
-                            const uint64_t adesc = A_MN_MAJOR ? make_smem_desc_sw128(sah + k * 4096, 1024, 1024)
-                                                              : make_smem_desc_sw128(sah + k * 32, 16, 1024);
-                            mma_i8_ss(d_tmem + h * kSkTileN, adesc, bdesc, idesc, (first && k == 0) ? 0u : 1u);
-                        }
+                    for (int h = 0; h < kSkHalves; ++h) {
+                        mma_i8_ss_warp(d_tmem + h * kSkTileN, desc64(a_lo + h * kAHalf + kAStep * k, kDescHi), bdesc,
+                                       idesc, accumulate);
                     }
-                    tc_commit(smem_u32(&tail->empty[stage]));
+                    accumulate = 1;
                 }
-                first = false;
-                __syncwarp();
+                tc_commit_warp(empty0 + stage * 8);
                 if (++stage == static_cast<uint32_t>(p.stages)) {
                     stage = 0;
                     phase ^= 1;
                 }
             }
-            if (ok && lane == 0) tc_commit(smem_u32(&tail->tmem_full[buf]));
-            __syncwarp();
+            if (ok) tc_commit_warp(smem_u32(&tail->tmem_full[buf]));
+            tile_end += p.kblocks;
             ++seg;
         }
     } else {

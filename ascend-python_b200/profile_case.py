@@ -28,6 +28,7 @@ def main():
     ap.add_argument("--algo", type=int, default=0)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--buffers", type=int, default=1, help="rotate over this many weight/input buffers")
+    ap.add_argument("--graph", action="store_true", help="also time the launches replayed from a CUDA graph")
     args = ap.parse_args()
     capi = load_package().capi
     dev = torch.device("cuda:0")
@@ -60,7 +61,29 @@ def main():
     e1.record()
     torch.cuda.synchronize()
     assert capi.device_status() == 0
-    print(f"{args.op} M={M} K={K} N={N}: {e0.elapsed_time(e1) / args.iters * 1e3:.1f} us per launch")
+    eager_us = e0.elapsed_time(e1) / args.iters * 1e3
+    graph_us = float("nan")
+    if args.graph:
+        # the same launches replayed from a CUDA graph: device time without the host's per-call cost
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            for i in range(3):
+                fn(i)
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(args.iters):
+                fn(i)
+        graph.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(5):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        graph_us = e0.elapsed_time(e1) / (5 * args.iters) * 1e3
+        assert capi.device_status() == 0
+    print(f"{args.op} M={M} K={K} N={N}: {eager_us:.1f} us per eager launch, {graph_us:.1f} us per launch in a graph")
 
 
 if __name__ == "__main__":
