@@ -355,6 +355,26 @@ __device__ __forceinline__ void mma_f16_ss_warp(uint32_t d_tmem, uint64_t a_desc
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// One 32-row step of two side-by-side accumulators: four MMAs (two k halves for each of d0, d1) and
+// the commit that releases the operands, all under one election.  The second k half always accumulates.
+__device__ __forceinline__ void mma_f16_ss_warp_2x2_commit(uint32_t d0, uint32_t d1, uint64_t a00, uint64_t a01,
+                                                           uint64_t a10, uint64_t a11, uint64_t b0, uint64_t b1,
+                                                           uint32_t idesc, uint32_t accumulate, uint32_t bar) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, e, t;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "setp.ne.b32 p, %9, 0;\n\t"
+        "setp.eq.b32 t, 0, 0;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %2, %6, %8, p;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%1], %4, %6, %8, p;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %3, %7, %8, t;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%1], %5, %7, %8, t;\n\t"
+        "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%10];\n\t"
+        "}\n" ::"r"(d0),
+        "r"(d1), "l"(a00), "l"(a01), "l"(a10), "l"(a11), "l"(b0), "l"(b1), "r"(idesc), "r"(accumulate), "r"(bar)
+        : "memory");
+}
 __device__ __forceinline__ void mma_i8_ss_pair_warp(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                                     uint32_t idesc, uint32_t accumulate) {
     asm volatile(

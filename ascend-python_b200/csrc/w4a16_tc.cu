@@ -8,24 +8,32 @@
 //
 // A work unit is 512 output columns x one quantization group.  512 columns are 256 contiguous
 // bytes of a packed weight row: narrower strips (the 64 bytes of a 128-column tile) leave HBM
-// with one short burst per DRAM page.  Per 16 k-rows a CTA
-//   1. receives the packed words [16 k][512 n / 8] (4 KiB) by TMA (the activations [M16][64 k]
+// with one short burst per DRAM page.  Per 32 k-rows (one step) a CTA
+//   1. receives the packed words [32 k][512 n / 8] (8 KiB) by TMA (the activations [M16][64 k]
 //      arrive once per 64 k-rows through their own ring),
-//   2. turns every packed word into eight 16-bit floats with four logic operations
+//   2. turns every packed word into eight 16-bit floats with a handful of logic operations
 //      (nibble | exponent bits = BIAS + w; for bf16 BIAS = 136 stays in the operand and is folded
 //      into the offset term, for f16 the constant 1032 is subtracted on the spot) and stores
 //      them as one 16-byte vector into the MN-major, 128-byte-swizzled A tiles,
-//   3. issues four 128 x M16 x 16 MMAs, one per 128-column sub-tile: weights are the M operand
+//   3. issues eight 128 x M16 x 16 MMAs, two per 128-column sub-tile: weights are the M operand
 //      (TMEM lane = output column, so row stores are coalesced), tokens padded to a multiple of
 //      16 are the N operand.
 // Within a 16-byte vector the columns appear in the order 0,4,1,5,2,6,3,7 (what the logic
 // operations produce without a shuffle); the epilogue maps lanes back to columns.
 //
-// Warp roles (832 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2-9
-// dequantization (two warps per 16-row step, four steps in flight), warps 10-25 per-group scaling
-// and epilogue (four warps per sub-tile).  Work is cut stream-K style into equal contiguous
-// ranges of (column unit, group); a unit shared by several CTAs is summed from per-CTA slots in
-// slot order by the last arriver, so results do not depend on arrival order.
+// The nibbles of a packed word belong to eight different output columns, while every tensor-core
+// operand format keeps consecutive k of ONE column together; the MN-major shared-memory layout is
+// what bridges the two.  Its price is shared-memory bandwidth: each weight is written as 2 bytes
+// and read back as 2 bytes by the MMA, next to the 0.5 byte that came from HBM, so the kernel is
+// bounded by the shared-memory pipe (about 5 bytes per weight at 128 bytes per clock and SM), not
+// by HBM.
+//
+// Warp roles (864 threads): warp 0 TMA producer; warps 1-2 MMA issuers (two sub-tiles each; warp 1
+// owns the TMEM allocation); warps 3-10 dequantization (two groups of four warps taking alternate
+// steps); warps 11-26 per-group scaling and epilogue (four warps per sub-tile).  Work is cut
+// stream-K style into equal contiguous ranges of (column unit, group); a unit shared by several
+// CTAs is summed from per-CTA slots in slot order by the last arriver, so results do not depend on
+// arrival order.
 #include "qmm_common.cuh"
 #include "w4a16_simt.cuh"
 
@@ -37,16 +45,24 @@ constexpr int kWTileN = 128;                 // columns per MMA (its M dimension
 constexpr int kWSub = 4;                     // MMAs side by side
 constexpr int kWUnitN = kWTileN * kWSub;     // 512 columns per work unit
 constexpr int kWBK = 64;                     // k rows per activation tile: one 128-byte swizzle row
-constexpr int kWStepK = 16;                  // k rows per weight stage = one MMA
-constexpr int kWPackedBytes = kWStepK * (kWUnitN / 8) * 4;  // 4 KiB of packed words per step
-constexpr int kWABytes = kWStepK * kWUnitN * 2;             // 16 KiB of dequantized A per step
-constexpr int kWASubBytes = kWABytes / kWSub;               // 4 KiB per sub-tile
-constexpr int kWABufs = 4;
-constexpr int kWStages = 16;                 // packed-weight stages (64 KiB in flight)
+constexpr int kWMmaK = 16;                   // k rows of one MMA
+constexpr int kWStepK = 32;                  // k rows per weight stage = two MMAs per sub-tile
+constexpr int kWPackedBytes = kWStepK * (kWUnitN / 8) * 4;  // 8 KiB of packed words per step
+constexpr int kWAHalfBytes = kWMmaK * kWUnitN * 2;          // 16 KiB of dequantized A per 16 k rows
+constexpr int kWABytes = (kWStepK / kWMmaK) * kWAHalfBytes; // 32 KiB per step
+constexpr int kWASubBytes = kWAHalfBytes / kWSub;           // 4 KiB per sub-tile and 16 k rows
+constexpr int kWABufs = 3;
+constexpr int kWStages = 8;                  // packed-weight stages (64 KiB in flight)
 constexpr int kWXStages = 4;                 // activation tiles
-constexpr int kWDeqWarps = 8;               // two warps per 16-row step
-constexpr int kWThreads = 64 + kWDeqWarps * 32 + 16 * 32;  // 832
+constexpr int kWMmaWarps = 2;                // each issues the MMAs of kWSub / kWMmaWarps sub-tiles
+constexpr int kWSubPerMma = kWSub / kWMmaWarps;
+constexpr int kWDeqGroups = 2;               // groups of dequantization warps taking alternate steps
+constexpr int kWDeqWarpsPerStep = 4;         // eight k rows of a step each
+constexpr int kWDeqWarps = kWDeqGroups * kWDeqWarpsPerStep;
 constexpr int kWEpiWarps = 16;
+constexpr int kWDeqFirstWarp = 1 + kWMmaWarps;
+constexpr int kWEpiFirstWarp = kWDeqFirstWarp + kWDeqWarps;
+constexpr int kWThreads = (kWEpiFirstWarp + kWEpiWarps) * 32;  // 864
 constexpr int kWMaxM = 64;
 constexpr int kWAccBufs = 2;                 // group accumulators in flight
 constexpr uint32_t kWTmemCols = 512;        // 2 buffers x 4 sub-tiles x up to 64 columns
@@ -74,7 +90,7 @@ struct WTcParams {
     int x_bytes;         // mpad * 128: one activation tile
     int units_n;         // 512-column units along N
     int ngroups;
-    int steps_per_group; // group / 16
+    int steps_per_group; // group / 32
     int max_slots;
     int xs_in_smem;      // the group sums fit the shared-memory area reserved for them
     const float *xsum;   // [ngroups][64]: sum over the group's k of x[m,k]

@@ -1,11 +1,11 @@
         // ---------------- scaling / epilogue warps (included inside w4a16_tc_kernel) ----------------
         // Four warps per 128-column sub-tile; thread = TMEM lane = one output column.  acc[m] collects,
         // group by group,  scale[g,n] * (P'[n,m] + (offset[g,n] - BIAS) * xsum[g,m]),  P' = sum_k (w + BIAS) * x.
-        const int sub = (warp - (2 + kWDeqWarps)) >> 2;                               // sub-tile of the 512-column unit
+        const int sub = (warp - kWEpiFirstWarp) >> 2;                               // sub-tile of the 512-column unit
         const int quarter = warp & 3;                                  // TMEM lanes [32*quarter, +32)
         const int row = quarter * 32 + lane;                           // lane of the accumulator
         const int n_local = (row & ~7) + ((row & 1) << 2) + ((row & 7) >> 1);  // undo the 0,4,1,5,2,6,3,7 order
-        const bool leader_thread = (threadIdx.x == (2 + kWDeqWarps) * 32);
+        const bool leader_thread = (threadIdx.x == kWEpiFirstWarp * 32);
         const W4Params &w = p.w;
         const T *scale = static_cast<const T *>(w.scale);
         const T *offset = static_cast<const T *>(w.offset);
@@ -17,7 +17,7 @@
         int64_t u = u_begin;
         // the group sums of x are read once per CTA into shared memory (broadcast reads afterwards)
         if (p.xs_in_smem) {
-            for (int i = threadIdx.x - (2 + kWDeqWarps) * 32; i < p.ngroups * p.mpad; i += kWEpiWarps * 32)
+            for (int i = threadIdx.x - kWEpiFirstWarp * 32; i < p.ngroups * p.mpad; i += kWEpiWarps * 32)
                 xs_smem[i] = __ldg(p.xsum + (i / p.mpad) * kWMaxM + (i % p.mpad));
             wepi_bar_sync();
         }
