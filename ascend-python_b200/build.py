@@ -73,7 +73,7 @@ def nccl_include_dir() -> Path | None:
 def build_kernels(force=False, verbose=False) -> Path:
     BUILD.mkdir(exist_ok=True)
     LIB.mkdir(exist_ok=True)
-    headers = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + [ROOT / "include" / "qmm_b200.h"]
+    headers = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.inl")) + list(CSRC.glob("*.h")) + [ROOT / "include" / "qmm_b200.h"]
     sources = sorted(CSRC.glob("*.cu"))
     flags = list(NVCC_FLAGS)
     inc = nccl_include_dir()

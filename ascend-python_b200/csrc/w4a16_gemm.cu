@@ -7,6 +7,10 @@ namespace qmm {
 bool w4a16_tc_supported(const W4Params &p, int x_dtype);
 size_t w4a16_tc_workspace_bytes(int64_t M, int64_t N, int64_t K, int64_t group);
 int launch_w4a16_tc(const W4Params &p, int x_dtype, void *workspace, cudaStream_t stream);
+// Implemented in w4a16_mma.cu: register-operand kernel for decode (M <= 16).
+bool w4a16_mma_supported(const W4Params &p, int x_dtype);
+size_t w4a16_mma_workspace_bytes(int64_t M, int64_t N, int64_t K, int64_t group);
+int launch_w4a16_mma(const W4Params &p, int x_dtype, void *workspace, cudaStream_t stream);
 }  // namespace qmm
 
 extern "C" int qmm_weight_quant_batchmatmul_workspace_size(int64_t M, int64_t N, int64_t K, int64_t group,
@@ -15,7 +19,9 @@ extern "C" int qmm_weight_quant_batchmatmul_workspace_size(int64_t M, int64_t N,
     QMM_REQUIRE(bytes != nullptr, "qmm_weight_quant_batchmatmul_workspace_size: bytes is NULL");
     QMM_REQUIRE(M >= 0 && N >= 0 && K >= 0 && group >= 0,
                 "qmm_weight_quant_batchmatmul_workspace_size: negative argument");
-    *bytes = w4a16_tc_workspace_bytes(M, N, K, group > 0 ? group : K);
+    const size_t tc = w4a16_tc_workspace_bytes(M, N, K, group > 0 ? group : K);
+    const size_t mma = w4a16_mma_workspace_bytes(M, N, K, group > 0 ? group : K);
+    *bytes = tc > mma ? tc : mma;
     return QMM_OK;
 }
 
@@ -56,7 +62,13 @@ extern "C" int qmm_weight_quant_batchmatmul(const void *x, int x_dtype, int64_t 
     p.N = N;
     p.K = K;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // tensor-core kernel when the operands meet TMA's 16-byte rules and scratch was provided
+    // Both tensor-core kernels need operands that meet TMA's 16-byte rules and 256-byte aligned
+    // scratch.  Up to 16 token rows the weights stay packed until they are in registers; beyond
+    // that the tcgen05 kernel takes over.
+    const bool ws_ok = workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255) == 0;
+    if (K > 0 && ws_ok && w4a16_mma_supported(p, x_dtype) &&
+        workspace_bytes >= w4a16_mma_workspace_bytes(M, N, K, p.group))
+        return launch_w4a16_mma(p, x_dtype, workspace, s);
     if (K > 0 && w4a16_tc_supported(p, x_dtype) && workspace != nullptr &&
         (reinterpret_cast<uintptr_t>(workspace) & 255) == 0 &&
         workspace_bytes >= w4a16_tc_workspace_bytes(M, N, K, p.group))
