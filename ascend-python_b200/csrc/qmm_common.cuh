@@ -105,9 +105,9 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 // Bounded wait on an mbarrier phase.  Returns false when the wait gave up or
 // when another thread of the CTA already did (abort flag in shared memory);
 // the caller then leaves its loop and falls through to the common teardown.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
-                                          uint32_t where) {
-    if (mbar_try_wait(bar, parity)) return true;
+// The slow path is kept out of line so that the hot loops carry one try_wait and one branch.
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                            uint32_t where) {
     const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
     while (true) {
@@ -120,6 +120,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             }
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                          uint32_t where) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, where);
 }
 
 // ---- TMA ------------------------------------------------------------------

@@ -16,13 +16,20 @@
 // The group sums of x that the offset term needs come from one more MMA per k block whose weight
 // operand is all ones, so they see exactly the rows (and the accumulation order) of the main sums.
 //
-// Roles (288 threads): warp 0 feeds a ring of 64-row stages by TMA (packed words as two
-// 128-byte-swizzled boxes of 32 words, plus the activation tile [8 or 16 tokens][64 k]); the eight
-// consumer warps form two sets of four (128 columns per warp) that take alternate quantization
-// groups, apply scale and offset to the group's accumulator in registers and keep the running
-// output in fp32 registers.  Work is cut stream-K style into equal contiguous ranges of
-// (512-column unit, group).  Every (CTA, set) writes its share of a unit to its own slot; the one
-// that arrives last adds the slots in slot order, so results do not depend on arrival order.
+// Roles: warp 0 feeds a ring of 64-row stages by TMA (packed words as two 128-byte-swizzled boxes
+// of 32 words, plus the activation tile [8 or 16 tokens][64 k]); the consumer warps form sets of
+// four (128 columns per warp) that take the quantization groups of the CTA's range in turn, apply
+// scale and offset to the group's accumulator in registers and keep the running output in fp32
+// (registers for up to 8 token rows with three sets; one private shared-memory column per thread
+// for 9..16 rows with two sets, which is what the register file allows).  Work is cut stream-K
+// style into equal contiguous ranges of (512-column unit, group).  Every (CTA, set) writes its
+// share of a unit to its own slot; the one that arrives last adds the slots in slot order, so
+// results do not depend on arrival order.
+//
+// The kernel is bounded by the integer/logic pipe (half rate): about one logic operation per weight
+// (pairing permutes, shifts, mask-and-flip), not by HBM and not by the tensor pipe.
+// QMM_W4_SETS and QMM_W4_YSMEM (1 = registers, 2 = shared memory) override the two choices above
+// for tuning.
 #include "qmm_common.cuh"
 #include "w4a16_simt.cuh"
 
@@ -146,13 +153,25 @@ struct GPlan {
     size_t slots_bytes;
 };
 
-// Sets per CTA: as many as the register file allows for the accumulators of MT token tiles.
+int g_env_int(const char *name) {
+    const char *e = std::getenv(name);
+    return e ? std::atoi(e) : 0;
+}
+
+// Whether the running outputs are kept in shared memory (frees 32 registers per token tile).
+bool g_outputs_in_smem(int mt) {
+    static const int forced = g_env_int("QMM_W4_YSMEM");  // 1: registers, 2: shared memory
+    if (forced == 1) return false;
+    if (forced == 2) return true;
+    return mt == 2;
+}
+
+// Consumer sets per CTA: as many as the register file allows.
 int g_sets_for(int mt) {
-    static const int forced = [] {
-        const char *e = std::getenv("QMM_W4_SETS");
-        return e ? std::atoi(e) : 0;
-    }();
-    if (forced >= 1 && forced <= (mt == 1 ? 3 : 2)) return forced;
+    static const int forced = g_env_int("QMM_W4_SETS");
+    const bool ys = g_outputs_in_smem(mt);
+    const int lo = 2, hi = mt == 1 ? (ys ? 4 : 3) : 2;  // bounded by registers and by shared memory
+    if (forced >= lo && forced <= hi) return forced;
     return mt == 1 ? 3 : 2;
 }
 
@@ -193,12 +212,24 @@ int launch_w4a16_mma_t(const W4Params &w, void *workspace, cudaStream_t stream) 
                       static_cast<uint64_t>(w.ld_x), kGStageK, static_cast<uint32_t>(8 * pl.mt), true);
     if (rc != QMM_OK) return rc;
 
-    const size_t smem = 1024 + static_cast<size_t>(kGStages) * kGStageBytes + sizeof(GSmemTail);
+    // stages, 1 KiB for the barriers, then (optionally) the running outputs of every consumer thread
+    const bool ys = g_outputs_in_smem(pl.mt);
+    static_assert(sizeof(GSmemTail) <= 1024, "the tail has 1 KiB");
+    const size_t smem = 1024 + static_cast<size_t>(kGStages) * kGStageBytes + 1024 +
+                        (ys ? static_cast<size_t>(32 * pl.mt) * pl.sets * kGColWarps * 32 * sizeof(float) : 0);
     void (*kern)(CUtensorMap, CUtensorMap, GParams) = nullptr;
-    if (pl.mt == 1)
-        kern = pl.sets == 3 ? w4a16_mma_kernel<T, 1, 3> : pl.sets == 2 ? w4a16_mma_kernel<T, 1, 2> : w4a16_mma_kernel<T, 1, 1>;
-    else
-        kern = pl.sets == 2 ? w4a16_mma_kernel<T, 2, 2> : w4a16_mma_kernel<T, 2, 1>;
+    if (pl.mt == 1) {
+        if (ys)
+            kern = pl.sets == 4 ? w4a16_mma_kernel<T, 1, 4, true> : pl.sets == 3 ? w4a16_mma_kernel<T, 1, 3, true>
+                                                                                 : w4a16_mma_kernel<T, 1, 2, true>;
+        else
+            kern = pl.sets == 3 ? w4a16_mma_kernel<T, 1, 3, false> : w4a16_mma_kernel<T, 1, 2, false>;
+    } else {
+        if (ys)
+            kern = w4a16_mma_kernel<T, 2, 2, true>;
+        else
+            kern = w4a16_mma_kernel<T, 2, 2, false>;
+    }
     QMM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     kern<<<pl.grid, (1 + pl.sets * kGColWarps) * 32, smem, stream>>>(tw, tx, p);
     QMM_CUDA_OK(cudaGetLastError());

@@ -2,8 +2,9 @@
 namespace qmm {
 namespace {
 
-// MT: token tiles of eight rows (1: M <= 8, 2: M <= 16); SETS: consumer sets taking the groups in turn
-template <typename T, int MT, int SETS>
+// MT: token tiles of eight rows (1: M <= 8, 2: M <= 16); SETS: consumer sets taking the groups in turn;
+// YS: the running outputs live in shared memory (one private column per thread) instead of registers
+template <typename T, int MT, int SETS, bool YS>
 __global__ void __launch_bounds__((1 + SETS * kGColWarps) * 32, 1)
 w4a16_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, GParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -95,6 +96,14 @@ w4a16_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         const uint32_t xoff = kGPackedBytes + gi * 128u + 4u * q;
 
         float y[MT][8][4];
+        // running outputs: registers, or [index][consumer thread] in shared memory (conflict-free)
+        float *ysm = reinterpret_cast<float *>(smem_aligned + kGStages * kGStageBytes + 1024) + (threadIdx.x - 32);
+        auto Y = [&](int mt, int j, int c) -> float & {
+            if constexpr (YS)
+                return ysm[((mt * 8 + j) * 4 + c) * (SETS * kGColWarps * 32)];
+            else
+                return y[mt][j][c];
+        };
         float acc[MT][8][4];
         float accx[MT][4];
         const uint32_t ones[4] = {GMagic<T>::kOnes, GMagic<T>::kOnes, GMagic<T>::kOnes, GMagic<T>::kOnes};
@@ -117,7 +126,7 @@ w4a16_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) y[mt][j][c] = 0.0f;
+                    for (int c = 0; c < 4; ++c) Y(mt, j, c) = 0.0f;
 
             // first item of this set in the segment: local indices are counted from u_begin
             int64_t it = seg_begin + ((set - (seg_begin - u_begin)) % SETS + SETS) % SETS;
@@ -213,7 +222,7 @@ w4a16_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         for (int c = 0; c < 4; ++c) {
                             const int r = c >> 1;  // which run of columns
                             const float xs = accx[mt][c & 1];
-                            y[mt][j][c] = fmaf(sf[r][j], fmaf(of[r][j], xs, acc[mt][j][c]), y[mt][j][c]);
+                            Y(mt, j, c) = fmaf(sf[r][j], fmaf(of[r][j], xs, acc[mt][j][c]), Y(mt, j, c));
                         }
             }
 
@@ -236,9 +245,9 @@ w4a16_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     if (token < M) {
                         float *dst = mine + token * kGUnitN + col + (c >> 1) * 64;
                         __stcg(reinterpret_cast<float4 *>(dst),
-                               make_float4(y[mt][0][c], y[mt][1][c], y[mt][2][c], y[mt][3][c]));
+                               make_float4(Y(mt, 0, c), Y(mt, 1, c), Y(mt, 2, c), Y(mt, 3, c)));
                         __stcg(reinterpret_cast<float4 *>(dst) + 1,
-                               make_float4(y[mt][4][c], y[mt][5][c], y[mt][6][c], y[mt][7][c]));
+                               make_float4(Y(mt, 4, c), Y(mt, 5, c), Y(mt, 6, c), Y(mt, 7, c)));
                     }
                 }
             __threadfence();
