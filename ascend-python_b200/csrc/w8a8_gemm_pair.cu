@@ -31,7 +31,6 @@ constexpr int kPAStageBytes = kPM * kPK;
 constexpr int kPBStageBytes = (kPN / 2) * kPK;
 constexpr int kPStageBytes = kPAStageBytes + kPBStageBytes;  // per CTA
 constexpr int kPThreads = 192;
-constexpr int kPGroupM = 8;  // pair-tiles (256 rows each) per rasterization group
 constexpr uint32_t kPTmemCols = 512;
 constexpr int kPEpiWarps = 4;
 constexpr int kPEpiStageBytes = 2 * 4096;
@@ -50,21 +49,71 @@ constexpr size_t kPairSmemBytes = kPStages * kPStageBytes + kPEpiWarps * kPEpiSt
                                   kPEpiWarps * kPEpiColFloats * sizeof(float) + sizeof(PairSmemTail);
 static_assert(kPairSmemBytes <= 232448, "pair kernel exceeds the 227 KiB of shared memory a CTA may use");
 
-__device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int &m_blk, int &n_blk) {
-    const int per_group = kPGroupM * tiles_n;
-    const int g = tile / per_group;
-    const int first_m = g * kPGroupM;
-    const int rows = min(kPGroupM, tiles_m - first_m);
-    const int r = tile - g * per_group;
-    m_blk = first_m + r % rows;
-    n_blk = r / rows;
+// Tile order.  raster > 0: groups of `raster` tile rows, each swept across all tile columns with the
+// rows running fastest, so the group's rows of A stay in L2 while B streams through once per group;
+// raster < 0: the same with the roles of rows and columns exchanged (-raster tile columns of B stay).
+__device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int raster, int &m_blk,
+                                                 int &n_blk) {
+    if (raster > 0) {
+        const int per_group = raster * tiles_n;
+        const int g = tile / per_group;
+        const int first_m = g * raster;
+        const int rows = min(raster, tiles_m - first_m);
+        const int r = tile - g * per_group;
+        m_blk = first_m + r % rows;
+        n_blk = r / rows;
+    } else {
+        const int gc = -raster;
+        const int per_group = gc * tiles_m;
+        const int g = tile / per_group;
+        const int first_n = g * gc;
+        const int cols = min(gc, tiles_n - first_n);
+        const int r = tile - g * per_group;
+        n_blk = first_n + r % cols;
+        m_blk = r / cols;
+    }
+}
+
+// Chooses the order that moves fewer bytes from DRAM.  With g tile rows (or columns) per group the
+// group's share of one operand stays in L2 while the other streams through once per group.  That
+// only works while the resident share, the part of the streaming operand that one wave of tiles
+// touches and the wave's outputs fit the L2 capacity seen by data that every SM reads (about half of
+// the 126 MB: each die keeps its own copy); when no group size fits, the smallest footprint wins.
+int pair_choose_raster(int64_t M, int64_t N, int64_t K, int64_t out_elt, int wave_tiles) {
+    const int64_t tiles_m = (M + 2 * kPM - 1) / (2 * kPM), tiles_n = (N + kPN - 1) / kPN;
+    const int64_t row_bytes = 2ll * kPM * K, col_bytes = static_cast<int64_t>(kPN) * K;
+    const int64_t out_bytes = static_cast<int64_t>(wave_tiles) * 2 * kPM * kPN * out_elt;
+    const int64_t capacity = 60ll << 20;
+    const int64_t a_total = M * K, b_total = N * K;
+    int best = 1;
+    int64_t best_traffic = -1, best_foot = -1;
+    bool best_fits = false;
+    auto consider = [&](int64_t g, bool rows) {
+        const int64_t tiles_g = rows ? tiles_m : tiles_n;
+        const int64_t across = (wave_tiles + g - 1) / g;  // tiles of the streaming operand per wave
+        const int64_t foot = g * (rows ? row_bytes : col_bytes) + across * (rows ? col_bytes : row_bytes) + out_bytes;
+        const int64_t traffic = rows ? a_total + (tiles_g + g - 1) / g * b_total
+                                     : b_total + (tiles_g + g - 1) / g * a_total;
+        const bool fits = foot <= capacity;
+        const bool better = best_traffic < 0 || (fits && !best_fits) ||
+                            (fits == best_fits && (fits ? traffic < best_traffic : foot < best_foot));
+        if (better) {
+            best = rows ? static_cast<int>(g) : -static_cast<int>(g);
+            best_traffic = traffic;
+            best_foot = foot;
+            best_fits = fits;
+        }
+    };
+    for (int64_t g = 1; g <= tiles_m; ++g) consider(g, true);
+    for (int64_t g = 1; g <= tiles_n; ++g) consider(g, false);
+    return best;
 }
 
 template <typename OutT, bool B_MN_MAJOR>
 __global__ void __launch_bounds__(kPThreads, 1)
 w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_out, EpilogueParams ep, int K, int use_tma_store,
-                 uint32_t *status) {
+                 int raster, uint32_t *status) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t smem_base = smem_u32(smem_raw);
     const uint32_t cta_rank = cluster_ctarank();  // 0 = leader
@@ -120,7 +169,7 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         bool ok = true;
         for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
             int m_blk, n_blk;
-            pair_tile_coords(tile, tiles_m, tiles_n, m_blk, n_blk);
+            pair_tile_coords(tile, tiles_m, tiles_n, raster, m_blk, n_blk);
             const int m0 = m_blk * 2 * kPM + static_cast<int>(cta_rank) * kPM;
             const int n0 = n_blk * kPN + static_cast<int>(cta_rank) * (kPN / 2);
             for (int kb = 0; kb < num_kb; ++kb) {
@@ -201,7 +250,7 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (lane == 0 && use_tma_store) tma_prefetch_desc(&tmap_out);
         for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++local) {
             int m_blk, n_blk;
-            pair_tile_coords(tile, tiles_m, tiles_n, m_blk, n_blk);
+            pair_tile_coords(tile, tiles_m, tiles_n, raster, m_blk, n_blk);
             const uint32_t buf = local & 1;
             const uint32_t buf_phase = (local >> 1) & 1;
             ok = mbar_wait(smem_u32(&tail->tmem_full[buf]), buf_phase, abort_flag, 0x24);
@@ -284,7 +333,8 @@ int launch_pair_t(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    QMM_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ta, tb, tout, ep, static_cast<int>(K), use_tma_store, status));
+    const int raster = pair_choose_raster(ep.M, ep.N, K, static_cast<int64_t>(sizeof(OutT)), pairs);
+    QMM_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ta, tb, tout, ep, static_cast<int>(K), use_tma_store, raster, status));
     return QMM_OK;
 }
 

@@ -35,6 +35,9 @@ sys.path.insert(0, str(ROOT))
 PREFILL_M = 8192
 PREFILL_GEMMS = [("qkv", 4096, 6144), ("gate_up", 4096, 28672), ("o_proj", 4096, 4096), ("down", 14336, 4096)]
 ROWPAR = dict(M=4096, K=28672, N=8192)
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of w8a8_pair_kernel per prefill shape (K, N), from ncu
+PAIR_DRAM_BYTES = {(4096, 6144): 65926656 + 69236736, (4096, 28672): 203958272 + 439107328,
+                   (4096, 4096): 53308928 + 34690816, (14336, 4096): 510722048 + 59542528}
 NOMINAL_INT8_TOPS = 4500.0  # NVIDIA's B200 dense int8 figure (9 POPS with 2:4 sparsity / 2)
 NOMINAL_HBM_GBS = 8000.0
 
@@ -300,7 +303,10 @@ def run_prefill(args, pkg, dev):
     achieved = total_ops / (gemm_ms * 1e-3) / 1e12
     int8_peak = 2.0 * peaks["bf16_sustained"]
     roofline = {"bound": "tensor", "kernel": "w8a8_pair_kernel", "achieved": achieved, "peak": int8_peak,
-                "unit": "TFLOP/s", "frac": achieved / int8_peak, "traffic": None,
+                "unit": "TFLOP/s", "frac": achieved / int8_peak, "traffic": sum(PAIR_DRAM_BYTES.values()),
+                "traffic_note": "dram read+write bytes of one ncu-captured launch per shape, summed over the four "
+                                "launches of a step (profiles/w8a8_pair_kernel_prefill_8b.md)",
+                "algorithmic_bytes": sum(M * L["K"] + L["K"] * L["N"] + 2 * M * L["N"] for L in layers),
                 "peak_note": f"2 x {peaks['source']} sustained bf16 cuBLAS throughput (int8 MMA issues at twice the "
                              "bf16 rate); no int8 figure is in MEASURED_PEAKS.json",
                 "frac_of_nominal_4500": achieved / NOMINAL_INT8_TOPS, "per_shape": per_shape}

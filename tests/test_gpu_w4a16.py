@@ -30,10 +30,12 @@ def _assert_close(y, y_ref, dtype):
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("shape", [(1, 256, 64, 128), (4, 256, 64, 128), (16, 1024, 512, 128), (64, 2048, 1024, 128),
                                    (3, 512, 136, 64), (17, 384, 128, 32), (130, 512, 256, 128), (8, 512, 256, 512),
-                                   (33, 4096, 7168, 128), (5, 8192, 2048 + 32, 128), (64, 1024, 4096, 1024)])
+                                   (33, 4096, 7168, 128), (5, 8192, 2048 + 32, 128), (64, 1024, 4096, 1024),
+                                   (9, 1024, 520, 64), (12, 256, 8, 256), (16, 2048, 1024 + 72, 128)])
 def test_against_oracle(capi, oracle, dev, shape, dtype, tensor_cores):
-    """tensor_cores=True passes the scratch buffer (tcgen05 kernel where the operands allow it: group a
-    multiple of 64, 16-byte pitches); False withholds it, which selects the CUDA-core kernel."""
+    """tensor_cores=True passes the scratch buffer (where the operands allow it -- group a multiple of 64,
+    16-byte pitches -- the register-operand MMA kernel up to 16 token rows and the tcgen05 kernel beyond);
+    False withholds it, which selects the CUDA-core kernel."""
     M, K, N, group = shape
     x, packed, scale, offset = oracle.make_w4a16_inputs(M, K, N, seed=M + K + N, group=group, dtype=dtype)
     y_ref = oracle.weight_quant_batchmatmul(x, packed, scale, offset, antiquant_group_size=group)
