@@ -64,6 +64,7 @@ struct GParams {
     int ngroups;
     int stages_per_group;  // group / 64
     int max_slots;         // slots per unit (CTAs sharing a unit x sets)
+    int nstages;           // stages of the ring actually used (shared memory permitting)
     float *slots;          // [units_n][max_slots][8 * MT][512]
     uint32_t *counters;    // [units_n], zero between calls
     uint32_t *status;
@@ -170,7 +171,7 @@ bool g_outputs_in_smem(int mt) {
 int g_sets_for(int mt) {
     static const int forced = g_env_int("QMM_W4_SETS");
     const bool ys = g_outputs_in_smem(mt);
-    const int lo = 2, hi = mt == 1 ? (ys ? 4 : 3) : 2;  // bounded by registers and by shared memory
+    const int lo = 2, hi = mt == 1 ? (ys ? 4 : 3) : (ys ? 3 : 2);  // bounded by registers and by shared memory
     if (forced >= lo && forced <= hi) return forced;
     return mt == 1 ? 3 : 2;
 }
@@ -212,11 +213,15 @@ int launch_w4a16_mma_t(const W4Params &w, void *workspace, cudaStream_t stream) 
                       static_cast<uint64_t>(w.ld_x), kGStageK, static_cast<uint32_t>(8 * pl.mt), true);
     if (rc != QMM_OK) return rc;
 
-    // stages, 1 KiB for the barriers, then (optionally) the running outputs of every consumer thread
+    // stages, 1 KiB for the barriers, then (optionally) the running outputs of every consumer thread;
+    // the ring gives up stages when the outputs need the room
     const bool ys = g_outputs_in_smem(pl.mt);
     static_assert(sizeof(GSmemTail) <= 1024, "the tail has 1 KiB");
-    const size_t smem = 1024 + static_cast<size_t>(kGStages) * kGStageBytes + 1024 +
-                        (ys ? static_cast<size_t>(32 * pl.mt) * pl.sets * kGColWarps * 32 * sizeof(float) : 0);
+    const size_t ys_bytes = ys ? static_cast<size_t>(32 * pl.mt) * pl.sets * kGColWarps * 32 * sizeof(float) : 0;
+    int nstages = kGStages;
+    while (nstages > 4 && 1024 + static_cast<size_t>(nstages) * kGStageBytes + 1024 + ys_bytes > 232448) --nstages;
+    p.nstages = nstages;
+    const size_t smem = 1024 + static_cast<size_t>(nstages) * kGStageBytes + 1024 + ys_bytes;
     void (*kern)(CUtensorMap, CUtensorMap, GParams) = nullptr;
     if (pl.mt == 1) {
         if (ys)
@@ -226,7 +231,7 @@ int launch_w4a16_mma_t(const W4Params &w, void *workspace, cudaStream_t stream) 
             kern = pl.sets == 3 ? w4a16_mma_kernel<T, 1, 3, false> : w4a16_mma_kernel<T, 1, 2, false>;
     } else {
         if (ys)
-            kern = w4a16_mma_kernel<T, 2, 2, true>;
+            kern = pl.sets == 3 ? w4a16_mma_kernel<T, 2, 3, true> : w4a16_mma_kernel<T, 2, 2, true>;
         else
             kern = w4a16_mma_kernel<T, 2, 2, false>;
     }

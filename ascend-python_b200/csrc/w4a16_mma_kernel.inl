@@ -10,7 +10,8 @@ w4a16_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
-    GSmemTail *tail = reinterpret_cast<GSmemTail *>(smem_aligned + kGStages * kGStageBytes);
+    const uint32_t nstages = static_cast<uint32_t>(p.nstages);  // ring length actually used
+    GSmemTail *tail = reinterpret_cast<GSmemTail *>(smem_aligned + nstages * kGStageBytes);
     volatile uint32_t *abort_flag = &tail->abort_flag;
 
     const int warp = threadIdx.x >> 5;
@@ -23,7 +24,7 @@ w4a16_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const W4Params &w = p.w;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kGStages; ++s) {
+        for (uint32_t s = 0; s < nstages; ++s) {
             mbar_init(smem_u32(&tail->full[s]), 1);
             mbar_init(smem_u32(&tail->empty[s]), kGColWarps);
         }
@@ -58,7 +59,7 @@ w4a16_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     tma_load_2d(dst + kGPackedBytes, &tmap_x, k0, 0, full0 + st * 8);  // [8 MT tokens][64 k]
                 }
                 __syncwarp();
-                if (++st == kGStages) {
+                if (++st == nstages) {
                     st = 0;
                     ph ^= 1;
                 }
@@ -97,7 +98,7 @@ w4a16_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
         float y[MT][8][4];
         // running outputs: registers, or [index][consumer thread] in shared memory (conflict-free)
-        float *ysm = reinterpret_cast<float *>(smem_aligned + kGStages * kGStageBytes + 1024) + (threadIdx.x - 32);
+        float *ysm = reinterpret_cast<float *>(smem_aligned + nstages * kGStageBytes + 1024) + (threadIdx.x - 32);
         auto Y = [&](int mt, int j, int c) -> float & {
             if constexpr (YS)
                 return ysm[((mt * 8 + j) * 4 + c) * (SETS * kGColWarps * 32)];
@@ -155,8 +156,8 @@ w4a16_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 const uint32_t step0 = static_cast<uint32_t>(it - u_begin) * static_cast<uint32_t>(spg);
                 for (int s = 0; s < spg; ++s) {
                     const uint32_t step = step0 + s;
-                    const uint32_t st = step % kGStages;
-                    const uint32_t ph = (step / kGStages) & 1u;
+                    const uint32_t st = step % nstages;
+                    const uint32_t ph = (step / nstages) & 1u;
                     if (ok && !mbar_wait(smem_u32(&tail->full[st]), ph, abort_flag, 0x41)) ok = false;
                     const uint8_t *sb = smem_aligned + st * kGStageBytes;
 #pragma unroll
