@@ -27,7 +27,8 @@ EXPORTED_SYMBOLS = (
     "qmm_quant_matmul_workspace_size", "qmm_quant_matmul", "qmm_weight_quant_batchmatmul_workspace_size",
     "qmm_weight_quant_batchmatmul",
     "qmm_comm_unique_id", "qmm_comm_init_rank", "qmm_comm_register", "qmm_comm_info", "qmm_comm_destroy",
-    "qmm_mm_all_reduce", "qmm_quant_matmul_decode_noalloc",
+    "qmm_mm_all_reduce", "qmm_quant_matmul_decode_noalloc", "qmm_comm_peer_memory_size",
+    "qmm_comm_attach_peer_memory",
 )
 NOALLOC_SCRATCH_BYTES = 16 << 20
 
@@ -94,6 +95,8 @@ def lib() -> ctypes.CDLL:
         L.qmm_comm_register.argtypes = [c.c_char_p, c.c_void_p, c.c_int, c.c_int]
         L.qmm_comm_info.argtypes = [c.c_char_p, c.POINTER(c.c_int), c.POINTER(c.c_int)]
         L.qmm_comm_destroy.argtypes = [c.c_char_p]
+        L.qmm_comm_peer_memory_size.argtypes = [c.c_int64, c.c_int64, c.c_int, c.POINTER(c.c_size_t)]
+        L.qmm_comm_attach_peer_memory.argtypes = [c.c_char_p, c.POINTER(c.c_void_p), c.c_void_p, c.c_size_t]
         L.qmm_mm_all_reduce.argtypes = [c.c_void_p, c.c_int64, c.c_void_p, c.c_int64, c.c_int64, c.c_void_p,
                                         c.c_int64, c.c_void_p, c.c_void_p, c.c_int, c.c_void_p, c.c_int, c.c_int64,
                                         c.c_int64, c.c_int64, c.c_int64, c.c_char_p, c.c_char_p, c.c_int64,

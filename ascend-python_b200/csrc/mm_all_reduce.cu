@@ -13,6 +13,10 @@
 // stream, an event hands the finished rows to the communication stream, whose
 // in-place ncclAllReduce of chunk c runs while chunk c+1 is being multiplied.
 // The matmul leaves a few SMs free while a collective may be in flight.
+//
+// When the ranks have attached peer memory to the communicator (qmm_comm_attach_peer_memory) and the
+// call fits it, NCCL is not involved: the matmul writes its partial output into this rank's region
+// and one kernel per rank (peer_all_reduce.cuh) reduces and gathers over NVLink loads.
 #include <dlfcn.h>
 #include <nccl.h>
 
@@ -20,6 +24,7 @@
 #include <mutex>
 #include <vector>
 
+#include "peer_all_reduce.cuh"
 #include "qmm_common.cuh"
 #include "w8a8_epilogue.cuh"
 
@@ -112,7 +117,16 @@ int comm_ctas() {
     return n;
 }
 
+// Regions of all ranks of the node as mapped into this process, for the peer-memory allreduce.
+struct PeerMem {
+    uint8_t *base[kPeerMaxRanks] = {};
+    uint8_t *mc_base = nullptr;  // the same regions through the NVLink multicast mapping, if there is one
+    size_t bytes = 0;     // size of every region
+    uint32_t epoch = 0;   // number of allreduce calls made through the regions
+};
+
 struct Comm {
+    PeerMem peer;
     ncclComm_t comm = nullptr;
     int nranks = 0;
     int rank = 0;
@@ -230,6 +244,77 @@ extern "C" int qmm_comm_register(const char *name, void *nccl_comm, int nranks, 
     return QMM_OK;
 }
 
+namespace qmm {
+namespace {
+
+size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+// Bytes of a region that an allreduce of [M][N] 16-bit values over `world` ranks needs.
+size_t peer_region_bytes(int64_t M, int64_t N, int world) {
+    (void)world;
+    return kPeerFlagBytes + 2 * align256(static_cast<size_t>(M) * N * 2);  // flags, partial, reduced
+}
+
+// Row chunks of the peer-memory path (QMM_PEER_CHUNKS, 1..8).
+int peer_chunks() {
+    static const int n = [] {
+        const char *e = getenv("QMM_PEER_CHUNKS");
+        const int v = e ? atoi(e) : 1;
+        return v < 1 ? 1 : (v > 8 ? 8 : v);
+    }();
+    return n;
+}
+
+bool peer_path_disabled() {
+    static const bool off = [] {
+        const char *e = getenv("QMM_ALLREDUCE");
+        return e != nullptr && std::string(e) == "nccl";
+    }();
+    return off;
+}
+
+}  // namespace
+}  // namespace qmm
+
+extern "C" int qmm_comm_peer_memory_size(int64_t M, int64_t N, int nranks, size_t *bytes) {
+    using namespace qmm;
+    QMM_REQUIRE(bytes != nullptr, "qmm_comm_peer_memory_size: bytes is NULL");
+    QMM_REQUIRE(M >= 0 && N >= 0 && nranks >= 1, "qmm_comm_peer_memory_size: bad argument");
+    *bytes = peer_region_bytes(M, N, nranks);
+    return QMM_OK;
+}
+
+extern "C" int qmm_comm_attach_peer_memory(const char *name, const void *const *regions, const void *multicast,
+                                           size_t bytes) {
+    using namespace qmm;
+    QMM_REQUIRE(name != nullptr, "qmm_comm_attach_peer_memory: name is NULL");
+    QMM_REQUIRE(regions != nullptr || bytes == 0, "qmm_comm_attach_peer_memory: regions is NULL");
+    std::lock_guard<std::mutex> lock(g_comm_mutex);
+    auto it = g_comms.find(name);
+    if (it == g_comms.end())
+        return fail(QMM_ERR_NOT_FOUND, std::string("communicator '") + name + "' is not registered");
+    Comm &c = it->second;
+    if (bytes == 0) {  // detach
+        c.peer = PeerMem();
+        return QMM_OK;
+    }
+    QMM_REQUIRE(c.nranks <= kPeerMaxRanks, "qmm_comm_attach_peer_memory: at most 8 ranks");
+    QMM_REQUIRE(bytes >= kPeerFlagBytes, "qmm_comm_attach_peer_memory: region smaller than its flag area");
+    PeerMem pm;
+    for (int r = 0; r < c.nranks; ++r) {
+        QMM_REQUIRE(regions[r] != nullptr && (reinterpret_cast<uintptr_t>(regions[r]) & 255) == 0,
+                    "qmm_comm_attach_peer_memory: regions must be non-NULL and 256-byte aligned");
+        pm.base[r] = static_cast<uint8_t *>(const_cast<void *>(regions[r]));
+    }
+    QMM_REQUIRE((reinterpret_cast<uintptr_t>(multicast) & 255) == 0,
+                "qmm_comm_attach_peer_memory: the multicast address must be 256-byte aligned");
+    pm.mc_base = static_cast<uint8_t *>(const_cast<void *>(multicast));
+    pm.bytes = bytes;
+    pm.epoch = 0;
+    c.peer = pm;
+    return QMM_OK;
+}
+
 extern "C" int qmm_comm_info(const char *name, int *nranks, int *rank) {
     using namespace qmm;
     QMM_REQUIRE(name != nullptr, "qmm_comm_info: name is NULL");
@@ -288,6 +373,86 @@ extern "C" int qmm_mm_all_reduce(const int8_t *x1, int64_t ld_x1, const int8_t *
     QMM_CUDA_OK(cudaGetDevice(&dev));
     QMM_REQUIRE(dev == c.device, "qmm_mm_all_reduce: communicator belongs to another device");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+    // Peer-memory path: matmul into this rank's region, then one reduce + gather kernel.
+    if (c.nranks > 1 && c.nranks <= kPeerMaxRanks && comm_turn == 0 && !peer_path_disabled() && N % 8 == 0 &&
+        (reinterpret_cast<uintptr_t>(out) & 15) == 0 && c.peer.bytes >= peer_region_bytes(M, N, c.nranks)) {
+        // Row chunks: chunk c's reduce + gather kernel runs on the communication stream while chunk
+        // c+1 is multiplied on the caller's stream.  The two share the SMs: the collective's CTAs need
+        // registers and threads only, the matmul's CTAs all of the shared memory, so one of each fits an
+        // SM, and the NVLink transfers proceed under the tensor work.
+        int chunks = peer_chunks();
+        if (M < 512 * chunks) chunks = 1;
+        int64_t rows_chunk = (M + chunks - 1) / chunks;
+        rows_chunk = (rows_chunk + 255) / 256 * 256;
+        const size_t elt = 2;
+        const size_t red_area = kPeerFlagBytes + align256(static_cast<size_t>(M) * N * elt);
+        int ci = 0;
+        for (int64_t m0 = 0; m0 < M; m0 += rows_chunk, ++ci) {
+            const int64_t rows = (M - m0) < rows_chunk ? (M - m0) : rows_chunk;
+            const size_t row_bytes0 = static_cast<size_t>(m0) * N * elt;
+            uint32_t epoch = 0;
+            {
+                std::lock_guard<std::mutex> lock(g_comm_mutex);
+                auto it = g_comms.find(hcom);
+                if (it == g_comms.end())
+                    return fail(QMM_ERR_NOT_FOUND, std::string("communicator '") + hcom + "' is not registered");
+                epoch = ++it->second.peer.epoch;
+            }
+            PeerParams pp;
+            for (int r = 0; r < kPeerMaxRanks; ++r) pp.base[r] = c.peer.base[r];
+            pp.mc_base = c.peer.mc_base;
+            pp.world = c.nranks;
+            pp.rank = c.rank;
+            pp.epoch = epoch;
+            pp.M = rows;
+            pp.N = N;
+            pp.rows_per = (rows + c.nranks - 1) / c.nranks;
+            pp.partial_off = kPeerFlagBytes + row_bytes0;
+            pp.red_off = red_area + row_bytes0;
+            pp.out = static_cast<uint8_t *>(out) + row_bytes0;
+            pp.status = device_status_word();
+            EpilogueParams ep;
+            ep.scale = scale;
+            ep.pertoken_scale = pertoken_scale ? pertoken_scale + m0 : nullptr;
+            ep.bias = (c.rank == 0) ? bias : nullptr;  // bias enters the sum once
+            ep.bias_dtype = ep.bias ? bias_dtype : QMM_DTYPE_NONE;
+            ep.scale_is_scalar = (scale_len == 1 && N != 1) ? 1 : 0;
+            ep.out = c.peer.base[c.rank] + pp.partial_off;
+            ep.ld_out = N;
+            ep.M = rows;
+            ep.N = N;
+            rc = quant_matmul_dispatch(x1 + m0 * ld_x1, ld_x1, x2, x2_stride_k, x2_stride_n, ep, out_dtype, K,
+                                       K == 0 ? QMM_ALGO_SIMT : QMM_ALGO_AUTO, workspace, workspace_bytes, s);
+            if (rc != QMM_OK) return rc;
+            cudaStream_t ks = s;
+            if (chunks > 1) {
+                QMM_CUDA_OK(cudaEventRecord(c.chunk_ready[ci], s));
+                QMM_CUDA_OK(cudaStreamWaitEvent(c.stream, c.chunk_ready[ci], 0));
+                ks = c.stream;
+            }
+            // every CTA must be resident (ranks wait on one another's CTAs): one or two per SM
+            const int grid = sm_count() * (chunks > 1 ? 1 : 2);
+            const bool mc = pp.mc_base != nullptr;
+            if (out_dtype == QMM_DTYPE_BF16) {
+                if (mc)
+                    peer_all_reduce_kernel<__nv_bfloat16, true><<<grid, kPeerThreads, 0, ks>>>(pp);
+                else
+                    peer_all_reduce_kernel<__nv_bfloat16, false><<<grid, kPeerThreads, 0, ks>>>(pp);
+            } else {
+                if (mc)
+                    peer_all_reduce_kernel<__half, true><<<grid, kPeerThreads, 0, ks>>>(pp);
+                else
+                    peer_all_reduce_kernel<__half, false><<<grid, kPeerThreads, 0, ks>>>(pp);
+            }
+            QMM_CUDA_OK(cudaGetLastError());
+        }
+        if (chunks > 1) {
+            QMM_CUDA_OK(cudaEventRecord(c.done, c.stream));
+            QMM_CUDA_OK(cudaStreamWaitEvent(s, c.done, 0));
+        }
+        return QMM_OK;
+    }
 
     // Number of M chunks.  Measured on 2, 4 and 8 B200s (M=4096, N=8192): every extra ncclAllReduce call
     // costs tens of microseconds and a collective confined to the SMs the matmul leaves free runs far

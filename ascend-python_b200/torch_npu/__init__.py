@@ -56,6 +56,8 @@ def npu_weight_quant_batchmatmul(x, weight, antiquant_scale, antiquant_offset=No
 
 def npu_mm_all_reduce_base(x1, x2, hcom, *, reduce_op="sum", bias=None, antiquant_scale=None, antiquant_offset=None,
                            x3=None, dequant_scale=None, pertoken_scale=None, antiquant_group_size=0, comm_turn=0):
+    if comm_turn == 0 and x1.is_cuda:
+        _ensure_peer_memory(hcom, x1.numel() // max(x1.shape[-1], 1), x2.shape[-1], x1.device)
     return _ops.npu_mm_all_reduce_base(x1, x2, hcom, reduce_op=reduce_op, bias=bias, antiquant_scale=antiquant_scale,
                                        antiquant_offset=antiquant_offset, x3=x3, dequant_scale=dequant_scale,
                                        pertoken_scale=pertoken_scale, antiquant_group_size=antiquant_group_size,
@@ -97,10 +99,69 @@ def get_comm_name(group=None) -> str:
     dist.broadcast_object_list(payload, src=src, group=group)
     uid = ctypes.create_string_buffer(payload[0], _capi.UNIQUE_ID_BYTES)
     _capi.check(lib.qmm_comm_init_rank(name.encode(), uid, world_size, rank), "qmm_comm_init_rank")
-    _comm_names[name] = True
+    _comm_names[name] = dict(group=group, world=world_size, rank=rank)
     return name
+
+
+_peer_memory = {}  # communicator name -> dict(bytes, tensor, handle) or None when unavailable
+
+
+def _ensure_peer_memory(name: str, M: int, N: int, device) -> None:
+    """Gives the communicator ``name`` peer-mapped regions large enough for an allreduce of [M, N].
+
+    The regions come from torch's symmetric memory (one allocation per rank, mapped by all ranks of
+    the node); the library then reduces and gathers through NVLink loads instead of NCCL.  The first
+    call, and any call that needs a larger region, is collective: all ranks reach it with the same
+    M and N.  Where symmetric memory is not available the communicator silently stays on NCCL.
+    QMM_ALLREDUCE=nccl disables the path.
+    """
+    import os
+
+    info = _comm_names.get(name)
+    if not isinstance(info, dict) or os.environ.get("QMM_ALLREDUCE", "") == "nccl":
+        return
+    world = info["world"]
+    if world < 2 or world > 8:
+        return
+    lib = _capi.lib()
+    need = ctypes.c_size_t(0)
+    _capi.check(lib.qmm_comm_peer_memory_size(M, N, world, ctypes.byref(need)), "qmm_comm_peer_memory_size")
+    cur = _peer_memory.get(name, {})
+    if cur is None or (cur and cur["bytes"] >= need.value):
+        return
+    try:
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        nbytes = max(int(need.value), 32 << 20)
+        nbytes = (nbytes + (2 << 20) - 1) // (2 << 20) * (2 << 20)
+        if cur:
+            _capi.check(lib.qmm_comm_attach_peer_memory(name.encode(), None, None, 0), "qmm_comm_attach_peer_memory")
+            torch.cuda.synchronize(device)
+        buf = symm.empty(nbytes, dtype=torch.uint8, device=device)
+        handle = symm.rendezvous(buf, info["group"])
+        buf.zero_()
+        torch.cuda.synchronize(device)
+        dist.barrier(group=info["group"])  # every region is zero before anyone raises a flag in it
+        ptrs = (ctypes.c_void_p * world)(*[int(a) for a in handle.buffer_ptrs])
+        # In-switch reduction pays from four ranks on (with two, every byte would cross the switch and
+        # come back); QMM_ALLREDUCE=multimem / p2p force one or the other.
+        mode = os.environ.get("QMM_ALLREDUCE", "")
+        mc = int(getattr(handle, "multicast_ptr", 0) or 0)
+        if mode == "p2p" or (mode != "multimem" and world < 4):
+            mc = 0
+        _capi.check(lib.qmm_comm_attach_peer_memory(name.encode(), ptrs, ctypes.c_void_p(mc or None), nbytes),
+                    "qmm_comm_attach_peer_memory")
+        _peer_memory[name] = dict(bytes=nbytes, tensor=buf, handle=handle)
+    except Exception as exc:  # symmetric memory missing or refused: NCCL carries the allreduce
+        import warnings
+
+        warnings.warn(f"peer memory for communicator {name} unavailable ({exc!r}); using NCCL")
+        _peer_memory[name] = None
 
 
 def destroy_comm(name: str) -> None:
     if _comm_names.pop(name, None):
+        _peer_memory.pop(name, None)
         _capi.check(_capi.lib().qmm_comm_destroy(name.encode()), "qmm_comm_destroy")

@@ -520,17 +520,19 @@ def run_rowpar(args, pkg, dev, rank, world):
             "warmup": max(args.warmup, 3), "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "int8", "data": "synthetic",
             "config": {"workload": "w8a8_row_parallel_allreduce", "M": M, "K": K, "N": N, "k_per_rank": Kr,
-                       "step": "dynamic quant of the rank's shard + W8A8 matmul + NCCL allreduce of bf16 partials",
+                       "step": "dynamic quant of the rank's shard + W8A8 matmul + allreduce of bf16 partials "
+                               + ("(NCCL)" if os.environ.get("QMM_ALLREDUCE", "") == "nccl"
+                                  else "(one reduce+gather kernel per rank over peer memory; NCCL if unavailable)"),
                        "l2": f"inputs larger than L2: {(x.numel() * 2 + w.numel() + M * N * 2) / 1e6:.0f} MB per rank"},
             "clocks": clocks.summary(),
             "e2e": {"value": total_ops * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS",
                     "h2d_bytes_per_step": host_x.numel() * 2, "d2h_bytes_per_step": host_y.numel() * 2,
                     "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
-            "gpu_launches": args.steps * 2,
+            "gpu_launches": args.steps * 3,
             "roofline": {"bound": "tensor", "kernel": "w8a8_pair_kernel", "achieved": achieved, "peak": int8_peak,
                          "unit": "TFLOP/s", "frac": achieved / int8_peak, "traffic": None,
                          "peak_note": f"2 x {peaks['source']} sustained bf16 cuBLAS throughput"},
-            "overlap": {"gemm_ms": gemm_ms, "allreduce_ms": ar_ms, "step_ms": step_ms,
+            "overlap": {"gemm_ms": gemm_ms, "nccl_allreduce_ms": ar_ms, "step_ms": step_ms,
                         "allreduce_busbw_GB/s": 2 * (world - 1) / world * M * N * 2 / (ar_ms * 1e-3) / 1e9,
                         "roofline_ms": max(gemm_ms, ar_ms)},
             "cpu_baseline": None,

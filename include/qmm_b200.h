@@ -168,6 +168,7 @@ QMM_API int qmm_weight_quant_batchmatmul(const void *x, int x_dtype, int64_t ld_
                                          void *out, int64_t ld_out, int64_t M, int64_t N, int64_t K,
                                          void *workspace, size_t workspace_bytes, void *stream);
 
+
 /*
  * Communicator registry.  The reference passes a communicator NAME into its
  * fused matmul+collective kernels (`hcom`,
@@ -182,6 +183,20 @@ QMM_API int qmm_comm_init_rank(const char *name, const void *id, int nranks, int
 QMM_API int qmm_comm_register(const char *name, void *nccl_comm, int nranks, int rank);
 QMM_API int qmm_comm_info(const char *name, int *nranks, int *rank);
 QMM_API int qmm_comm_destroy(const char *name);
+
+/* Peer memory for the allreduce of qmm_mm_all_reduce (no counterpart in the reference: its device
+ * library owns the communication buffers behind the communicator name,
+ * op_plugin/ops/base_ops/opapi/MatmulReduceScatterBaseKernelNpuOpApi.cpp:35-40).
+ * Every rank of the node allocates a region of the same size, zero-filled, that all ranks map
+ * (CUDA IPC / symmetric memory), and hands the library the W addresses under which this process
+ * sees them, in rank order (its own included), plus - where the regions are bound to an NVLink
+ * multicast object - the multicast address (else NULL).  qmm_comm_peer_memory_size gives the size an
+ * allreduce of [M][N] 16-bit values needs.  While regions are attached and large enough, calls
+ * with comm_turn == 0 reduce and gather through NVLink loads in one kernel per rank instead of
+ * NCCL; the environment variable QMM_ALLREDUCE=nccl switches that off.  bytes == 0 detaches. */
+QMM_API int qmm_comm_peer_memory_size(int64_t M, int64_t N, int nranks, size_t *bytes);
+QMM_API int qmm_comm_attach_peer_memory(const char *name, const void *const *regions, const void *multicast,
+                                        size_t bytes);
 
 /*
  * Row-parallel W8A8 matmul + allreduce (torch op `npu_mm_all_reduce_base`;

@@ -1,5 +1,5 @@
 """npu_mm_all_reduce_base: a single-rank communicator on one GPU, and 2/4/8 ranks (one process per
-GPU, NCCL) when the box has that many GPUs.  Tolerance after the allreduce: rtol 1e-2 against the
+GPU; allreduce through peer memory or NCCL) when the box has that many GPUs.  Tolerance after the allreduce: rtol 1e-2 against the
 fp32 sum of the per-rank fp32 results (plus 1e-2 of the summed magnitudes as atol for cancellation)."""
 import ctypes
 import os
@@ -74,19 +74,26 @@ def _rank_main(rank, world, port, shapes, c2p):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 4, 8])
-def test_multi_rank(oracle, pkg, world):
+@pytest.mark.parametrize("world,path", [(2, "peer"), (2, "multimem"), (2, "nccl"), (4, "peer"), (8, "peer"), (8, "p2p")])
+def test_multi_rank(oracle, pkg, world, path):
+    """path "peer": calls with comm_turn == 0 reduce and gather through peer memory in the library's own
+    kernel (the default where symmetric memory is available; with in-switch reduction where the regions have
+    an NVLink multicast mapping and there are at least four ranks); "p2p" / "multimem" force plain peer loads /
+    in-switch reduction; "nccl" forces NCCL for every call."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     from ascend_python_b200.sharding import shard_row_parallel
 
-    shapes = [(256, 1024, 512, 0), (2048, 4096, 1024, 2), (1000, 2048, 768, 3)]
+    shapes = [(256, 1024, 512, 0), (2048, 4096, 1024, 2), (1000, 2048, 768, 3), (1000, 2048, 768, 0),
+              (2048, 4096, 1024, 0), (3, 512, 264, 0)]
     ctx = mp.get_context("spawn")
     c2p = ctx.Queue()
     port = 29700 + os.getpid() % 1000
     env = dict(os.environ)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
+    if path != "peer":
+        os.environ["QMM_ALLREDUCE"] = path
     try:
         procs = [ctx.Process(target=_rank_main, args=(r, world, port, shapes, c2p)) for r in range(world)]
         for p in procs:
