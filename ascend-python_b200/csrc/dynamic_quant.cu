@@ -9,9 +9,12 @@
 // Numerics (bit-exact contract with the CPU oracle):
 //   scale = amax / 127            IEEE fp32 division
 //   q     = rint(x / scale)       IEEE fp32 division, round half to even
-// The division x / scale is evaluated as x * (1/scale) when that provably
-// rounds to the same integer, and by a true division when the product lands
-// within 1e-4 of a rounding tie (product and quotient differ by < 2.3e-5).
+// The division x / scale runs on the FMA pipe: with y = RN(1/scale), q0 = RN(x*y), the exact
+// remainder r = fma(-q0, scale, x) and q1 = RN(q0 + r*y), q1 is the correctly rounded quotient
+// (Markstein's theorem: y correctly rounded, q0 within one ulp, no underflow, and the significand
+// of the divisor not all ones).  Rows whose scale breaks a precondition take true divisions.
+// bf16/f16 inputs make EXACT ties (x / scale = n + 1/2) common - x and amax are short-mantissa
+// numbers - so a scheme that falls back to a division near ties would fall back all the time.
 #include "qmm_common.cuh"
 
 namespace qmm {
@@ -53,19 +56,23 @@ __device__ __forceinline__ RowQuant make_row_quant(float amax) {
     RowQuant r;
     r.scale = __fdiv_rn(amax, 127.0f);
     r.inv = __frcp_rn(r.scale);
-    r.exact_only = !(r.scale >= 1e-30f) || !(r.inv <= 3.0e38f);
+    // preconditions of the FMA division: no underflow in the remainder, a finite reciprocal, and a
+    // divisor whose significand is not all ones
+    r.exact_only = !(r.scale >= 1e-25f) || !(r.inv <= 3.0e38f) ||
+                   (__float_as_uint(r.scale) & 0x007fffffu) == 0x007fffffu;
     return r;
 }
 
 __device__ __forceinline__ int quant_one(float x, const RowQuant &rq) {
     if (rq.scale == 0.0f) return 0;
-    float t = rq.exact_only ? __fdiv_rn(x, rq.scale) : x * rq.inv;
-    int q = __float2int_rn(t);
-    if (!rq.exact_only) {
-        float d = fabsf(t - static_cast<float>(q));
-        if (d > 0.499f) q = __float2int_rn(__fdiv_rn(x, rq.scale));
+    float t;
+    if (rq.exact_only) {
+        t = __fdiv_rn(x, rq.scale);
+    } else {
+        const float q0 = x * rq.inv;
+        t = fmaf(fmaf(-q0, rq.scale, x), rq.inv, q0);
     }
-    return max(-128, min(127, q));
+    return max(-128, min(127, __float2int_rn(t)));
 }
 
 // absmax of the eight 16-bit floats of a 128-bit vector, packed two at a time
@@ -144,27 +151,16 @@ dynamic_quant_vec_kernel(const T *__restrict__ x, int64_t rows, int cols, int64_
             unpack8<T>(v[i], f);
             uint32_t lo = 0, hi = 0;
             if (fast) {
-                // main path: four FMA-pipe operations per element, one max for the tie test
+                // main path, FMA pipe only: product, exact remainder, corrected quotient, magic-number rounding
                 constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23: adding it rounds to an integer, ties to even
-                float r[8];
-                float dmax = 0.0f;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const float t = f[j] * rq.inv;
-                    r[j] = t + kMagic;
-                    dmax = fmaxf(dmax, fabsf(t - (r[j] - kMagic)));
-                }
-                if (dmax > 0.4999f) {
-                    // some product lies within 1e-4 of a rounding tie: let the exact quotient decide there
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const float t = f[j] * rq.inv;
-                        if (fabsf(t - (r[j] - kMagic)) > 0.4999f) r[j] = rintf(__fdiv_rn(f[j], rq.scale)) + kMagic;
-                    }
-                }
                 uint32_t b[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) b[j] = __float_as_uint(r[j]);
+                for (int j = 0; j < 8; ++j) {
+                    const float q0 = f[j] * rq.inv;
+                    const float rem = fmaf(-q0, rq.scale, f[j]);
+                    const float q1 = fmaf(rem, rq.inv, q0);  // = RN(f / scale)
+                    b[j] = __float_as_uint(q1 + kMagic);
+                }
                 // the int8 results are the low bytes of the biased floats: gather (b0..b3) and (b4..b7)
                 lo = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
                 hi = __byte_perm(__byte_perm(b[4], b[5], 0x0040), __byte_perm(b[6], b[7], 0x0040), 0x5410);

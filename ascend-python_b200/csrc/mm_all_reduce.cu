@@ -37,6 +37,8 @@ int validate_quant_matmul(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int
                           const float *scale, int64_t scale_len, const void *bias, int bias_dtype, void *out,
                           int out_dtype, int64_t ld_out, int64_t M, int64_t N, int64_t K);
 void set_sm_reserve(int sms);
+void set_push_targets(const PushSpec *spec);
+bool push_applied();
 
 namespace {
 
@@ -251,8 +253,10 @@ size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
 // Bytes of a region that an allreduce of [M][N] 16-bit values over `world` ranks needs.
 size_t peer_region_bytes(int64_t M, int64_t N, int world) {
-    (void)world;
-    return kPeerFlagBytes + 2 * align256(static_cast<size_t>(M) * N * 2);  // flags, partial, reduced
+    // flags; partials, either [M][N] or [world][rows_per][N] with rows_per rounded up to 32; reduced [M][N]
+    const int64_t rows_per = ((M + world - 1) / world + 31) / 32 * 32;
+    return kPeerFlagBytes + align256(static_cast<size_t>(world) * rows_per * N * 2) +
+           align256(static_cast<size_t>(M) * N * 2);
 }
 
 // Row chunks of the peer-memory path (QMM_PEER_CHUNKS, 1..8).
@@ -263,6 +267,15 @@ int peer_chunks() {
         return v < 1 ? 1 : (v > 8 ? 8 : v);
     }();
     return n;
+}
+
+// QMM_PEER_PUSH=0 keeps the matmul's output local (the reduce kernel then pulls it over NVLink).
+bool push_disabled() {
+    static const bool off = [] {
+        const char *e = getenv("QMM_PEER_PUSH");
+        return e != nullptr && std::string(e) == "0";
+    }();
+    return off;
 }
 
 bool peer_path_disabled() {
@@ -386,7 +399,9 @@ extern "C" int qmm_mm_all_reduce(const int8_t *x1, int64_t ld_x1, const int8_t *
         int64_t rows_chunk = (M + chunks - 1) / chunks;
         rows_chunk = (rows_chunk + 255) / 256 * 256;
         const size_t elt = 2;
-        const size_t red_area = kPeerFlagBytes + align256(static_cast<size_t>(M) * N * elt);
+        const int64_t rows_per_full = ((M + c.nranks - 1) / c.nranks + 31) / 32 * 32;
+        const size_t red_area = kPeerFlagBytes + align256(static_cast<size_t>(c.nranks) * rows_per_full * N * elt);
+        const bool push_ok = chunks == 1 && !push_disabled();
         int ci = 0;
         for (int64_t m0 = 0; m0 < M; m0 += rows_chunk, ++ci) {
             const int64_t rows = (M - m0) < rows_chunk ? (M - m0) : rows_chunk;
@@ -407,7 +422,8 @@ extern "C" int qmm_mm_all_reduce(const int8_t *x1, int64_t ld_x1, const int8_t *
             pp.epoch = epoch;
             pp.M = rows;
             pp.N = N;
-            pp.rows_per = (rows + c.nranks - 1) / c.nranks;
+            pp.rows_per = chunks == 1 ? rows_per_full : (rows + c.nranks - 1) / c.nranks;
+            pp.pushed = 0;
             pp.partial_off = kPeerFlagBytes + row_bytes0;
             pp.red_off = red_area + row_bytes0;
             pp.out = static_cast<uint8_t *>(out) + row_bytes0;
@@ -422,8 +438,20 @@ extern "C" int qmm_mm_all_reduce(const int8_t *x1, int64_t ld_x1, const int8_t *
             ep.ld_out = N;
             ep.M = rows;
             ep.N = N;
+            // the CTA-pair matmul stores each output tile into the region of the rank that owns its rows
+            PushSpec spec;
+            if (push_ok) {
+                for (int r = 0; r < kPeerMaxRanks; ++r) spec.base[r] = c.peer.base[r];
+                spec.area_off = pp.partial_off;
+                spec.world = c.nranks;
+                spec.rank = c.rank;
+                spec.rows_per = pp.rows_per;
+                set_push_targets(&spec);
+            }
             rc = quant_matmul_dispatch(x1 + m0 * ld_x1, ld_x1, x2, x2_stride_k, x2_stride_n, ep, out_dtype, K,
                                        K == 0 ? QMM_ALGO_SIMT : QMM_ALGO_AUTO, workspace, workspace_bytes, s);
+            pp.pushed = push_applied() ? 1 : 0;
+            set_push_targets(nullptr);
             if (rc != QMM_OK) return rc;
             cudaStream_t ks = s;
             if (chunks > 1) {

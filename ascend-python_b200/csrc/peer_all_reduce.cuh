@@ -6,6 +6,10 @@
 // matmul kernel that ran just before on the same stream), the reduced output [M][N] (a rank fills
 // the rows it owns; with multicast, everybody's rows).
 //
+// The CTA-pair matmul can deliver its output tiles straight into the owners' regions (TMA stores to
+// peer memory from its epilogue), which moves the reduce-scatter traffic under the matmul; step 2
+// then reads local memory only.  Otherwise the partial stays in the producing rank's region.
+//
 //   1. the kernel tells every peer "my partial is complete" (flag A) and waits for theirs;
 //   2. rank r owns rows [r * rows_per, (r+1) * rows_per): it loads those rows of all W partials
 //      (its own from HBM, the others over NVLink), adds them in fp32 in rank order - so the result
@@ -47,6 +51,8 @@ struct PeerParams {
     uint32_t epoch;
     int64_t M, N;
     int64_t rows_per;              // rows owned by a rank (the last owner may hold fewer)
+    int pushed;                    // the matmul already delivered every rank's share of the rows this rank owns
+                                   // into this rank's region: [source rank][rows_per][N] in the partial area
     size_t partial_off, red_off;   // byte offsets of the two data areas inside a region
     void *out;                     // [M][N], this rank's result
     uint32_t *status;
@@ -150,7 +156,7 @@ __global__ void __launch_bounds__(kPeerThreads, 2) peer_all_reduce_kernel(PeerPa
     for (int c = blockIdx.x; c < kPeerChunks; c += gridDim.x) {
         int64_t lo, hi;
         chunk_bounds(own_vecs, c, lo, hi);
-        if constexpr (MC) {
+        if (MC && !p.pushed) {
             const uint8_t *mc_part = p.mc_base + p.partial_off + own_byte0;
             uint8_t *mc_red = p.mc_base + p.red_off + own_byte0;
             // four vectors per thread and pass, so that enough loads are in flight for the link latency
@@ -171,8 +177,12 @@ __global__ void __launch_bounds__(kPeerThreads, 2) peer_all_reduce_kernel(PeerPa
                 uint4 part[kPeerMaxRanks];  // all ranks' loads of a vector are in flight together
 #pragma unroll
                 for (int r = 0; r < kPeerMaxRanks; ++r)
-                    if (r < W)
-                        part[r] = __ldcg(reinterpret_cast<const uint4 *>(p.base[r] + p.partial_off + own_byte0) + v);
+                    if (r < W) {
+                        const uint8_t *src = p.pushed ? p.base[p.rank] + p.partial_off +
+                                                            static_cast<size_t>(r) * p.rows_per * p.N * sizeof(T)
+                                                      : p.base[r] + p.partial_off + own_byte0;
+                        part[r] = __ldcg(reinterpret_cast<const uint4 *>(src) + v);
+                    }
                 float acc[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
@@ -184,7 +194,10 @@ __global__ void __launch_bounds__(kPeerThreads, 2) peer_all_reduce_kernel(PeerPa
                 o.y = pack2<T>(acc[2], acc[3]);
                 o.z = pack2<T>(acc[4], acc[5]);
                 o.w = pack2<T>(acc[6], acc[7]);
-                red[v] = o;
+                if constexpr (MC)
+                    multimem_st(p.mc_base + p.red_off + own_byte0 + v * 16, o);
+                else
+                    red[v] = o;
                 out_own[v] = o;
             }
         }

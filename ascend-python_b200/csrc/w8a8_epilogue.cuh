@@ -23,6 +23,22 @@ struct EpilogueParams {
     int64_t N;
 };
 
+// Row-parallel matmul whose output tiles go straight to the rank that will reduce them: rank o owns the
+// rows [o * rows_per, (o+1) * rows_per) and receives them from rank s at
+// base[o] + area_off + s * rows_per * N * element size.  Host-side description (see set_push_targets).
+struct PushSpec {
+    uint8_t *base[8];
+    size_t area_off;
+    int world, rank;
+    int64_t rows_per;  // a multiple of 32, so the 32 rows of an epilogue warp have one owner
+};
+// Kernel-side form: one output tensor map per owner.
+struct PushMaps {
+    CUtensorMap m[8];
+    int64_t rows_per;
+    int enabled;
+};
+
 __device__ __forceinline__ float load_bias_f32(const EpilogueParams &p, int64_t n) {
     switch (p.bias_dtype) {
         case QMM_DTYPE_BF16:
@@ -133,7 +149,10 @@ struct EpiChunk {
 template <typename OutT, int TILE_N>
 __device__ __forceinline__ void epilogue_warp_tile_tma(const EpilogueParams &p, const CUtensorMap *tmap_out,
                                                        uint32_t taddr_warp, int64_t m_warp0, int64_t n_tile0,
-                                                       uint8_t *stage, float *colbuf, uint32_t &chunk_counter) {
+                                                       uint8_t *stage, float *colbuf, uint32_t &chunk_counter,
+                                                       int64_t store_row0 = -1) {
+    // store_row0: row coordinate of the warp's first row in tmap_out when that map does not start at
+    // row 0 of the output (tiles pushed into another rank's receive area); -1: same as m_warp0
     constexpr int CC = EpiChunk<OutT>::kCols;
     const int lane = threadIdx.x & 31;
     const int64_t m = m_warp0 + lane;
@@ -217,7 +236,8 @@ __device__ __forceinline__ void epilogue_warp_tile_tma(const EpilogueParams &p, 
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-            tma_store_2d(tmap_out, stage_u32 + buf * 4096, static_cast<int32_t>(n0), static_cast<int32_t>(m_warp0));
+            tma_store_2d(tmap_out, stage_u32 + buf * 4096, static_cast<int32_t>(n0),
+                         static_cast<int32_t>(store_row0 >= 0 ? store_row0 : m_warp0));
             tma_store_commit();
         }
         ++chunk_counter;

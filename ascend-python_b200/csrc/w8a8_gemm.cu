@@ -26,6 +26,19 @@ static thread_local int g_sm_reserve = 0;
 void set_sm_reserve(int sms) { g_sm_reserve = sms < 0 ? 0 : sms; }
 int pair_sm_reserve() { return g_sm_reserve; }
 
+// Push targets for the next quant_matmul_dispatch of this thread (set and cleared by the matmul +
+// allreduce operator).  Only the CTA-pair kernel honours them; push_applied() tells the caller whether
+// the launch that just happened did.
+static thread_local const PushSpec *g_push_spec = nullptr;
+static thread_local bool g_push_applied = false;
+void set_push_targets(const PushSpec *spec) {
+    g_push_spec = spec;
+    g_push_applied = false;
+}
+const PushSpec *pair_push_targets() { return g_push_spec; }
+void mark_push_applied() { g_push_applied = true; }
+bool push_applied() { return g_push_applied; }
+
 // Implemented in w8a8_gemm_pair.cu
 int launch_pair(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
                 const struct EpilogueParams &ep, int out_dtype, int64_t K, cudaStream_t stream);

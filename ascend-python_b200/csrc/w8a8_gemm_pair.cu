@@ -14,12 +14,16 @@
 //   tmem_full[b]  one per CTA; the leader's tcgen05.commit arrives on both
 //   tmem_empty[b] leader's barrier; the 4+4 epilogue warps of the pair arrive on it
 // No TMA load uses multicast; every wait is bounded (see mbar_wait).
+#include <cstring>
+
 #include "qmm_common.cuh"
 #include "w8a8_epilogue.cuh"
 
 namespace qmm {
 
 int pair_sm_reserve();  // SMs to leave idle (set by callers that overlap a collective)
+const PushSpec *pair_push_targets();  // owners' receive areas for the output tiles, or nullptr
+void mark_push_applied();
 
 namespace {
 
@@ -112,8 +116,8 @@ int pair_choose_raster(int64_t M, int64_t N, int64_t K, int64_t out_elt, int wav
 template <typename OutT, bool B_MN_MAJOR>
 __global__ void __launch_bounds__(kPThreads, 1)
 w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_out, EpilogueParams ep, int K, int use_tma_store,
-                 int raster, uint32_t *status) {
+                 const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ PushMaps push,
+                 EpilogueParams ep, int K, int use_tma_store, int raster, uint32_t *status) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t smem_base = smem_u32(smem_raw);
     const uint32_t cta_rank = cluster_ctarank();  // 0 = leader
@@ -259,8 +263,16 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const int64_t m_warp0 = static_cast<int64_t>(m_blk) * 2 * kPM + cta_rank * kPM + quarter * 32;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kPN;
             if (use_tma_store) {
-                epilogue_warp_tile_tma<OutT, kPN>(ep, &tmap_out, taddr, m_warp0, static_cast<int64_t>(n_blk) * kPN,
-                                                  my_stage, my_cols, chunk_counter);
+                // with push targets the tile goes to the receive area of the rank that owns its rows
+                const CUtensorMap *omap = &tmap_out;
+                int64_t store_row0 = -1;
+                if (push.enabled) {
+                    const int owner = static_cast<int>(m_warp0 / push.rows_per);
+                    omap = &push.m[owner];
+                    store_row0 = m_warp0 - owner * push.rows_per;
+                }
+                epilogue_warp_tile_tma<OutT, kPN>(ep, omap, taddr, m_warp0, static_cast<int64_t>(n_blk) * kPN,
+                                                  my_stage, my_cols, chunk_counter, store_row0);
             } else {
 #pragma unroll 1
                 for (int c = 0; c < kPN / 32; ++c) {
@@ -334,7 +346,31 @@ int launch_pair_t(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     const int raster = pair_choose_raster(ep.M, ep.N, K, static_cast<int64_t>(sizeof(OutT)), pairs);
-    QMM_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ta, tb, tout, ep, static_cast<int>(K), use_tma_store, raster, status));
+    PushMaps push;
+    memset(&push, 0, sizeof(push));
+    if (const PushSpec *ps = pair_push_targets()) {
+        if (use_tma_store && sizeof(OutT) == 2 && ps->rows_per % 32 == 0 && ep.ld_out == ep.N) {
+            for (int o = 0; o < ps->world; ++o) {
+                const int64_t row0 = static_cast<int64_t>(o) * ps->rows_per;
+                int64_t rows_o = ep.M - row0;
+                if (rows_o > ps->rows_per) rows_o = ps->rows_per;
+                if (rows_o <= 0) {  // this owner holds no rows: never addressed, keep a valid map
+                    push.m[o] = tout;
+                    continue;
+                }
+                uint8_t *dst = ps->base[o] + ps->area_off +
+                               static_cast<size_t>(ps->rank) * ps->rows_per * ep.N * sizeof(OutT);
+                rc = make_tmap_2d(&push.m[o], dst, kElt, static_cast<uint64_t>(ep.N), static_cast<uint64_t>(rows_o),
+                                  static_cast<uint64_t>(ep.N), 128 / kElt, 32, true);
+                if (rc != QMM_OK) return rc;
+            }
+            push.rows_per = ps->rows_per;
+            push.enabled = 1;
+            mark_push_applied();
+        }
+    }
+    QMM_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ta, tb, tout, push, ep, static_cast<int>(K), use_tma_store, raster,
+                                   status));
     return QMM_OK;
 }
 

@@ -52,6 +52,28 @@ def test_value_edge_cases(capi, oracle, dev):
     _check(capi, oracle, (base * 0.37).to(torch.float16), dev)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_every_mantissa_against_every_maximum(capi, oracle, dev, dtype):
+    """Short-mantissa inputs make exact ties x / scale = n + 1/2 common.  Row r has the maximum (128 + r) / 64
+    and holds every 8-bit significand at eight exponents and both signs, so all ratios x / amax of two such
+    numbers occur - ties, near ties and all; results must equal the IEEE divisions of the oracle bit for bit."""
+    mant = torch.arange(128, 256, dtype=torch.float32)
+    exps = torch.tensor([2.0 ** -e for e in range(6, 14)])
+    vals = (mant[None, :] * exps[:, None]).reshape(-1)            # 1024 values in (0, 4)
+    vals = torch.cat([vals, -vals])                                # 2048 columns
+    rows = []
+    for r in range(128):
+        amax = (128 + r) / 64.0
+        row = vals.clamp(-amax, amax).clone()
+        row[0] = amax
+        rows.append(row)
+    x = torch.stack(rows).to(dtype)
+    _check(capi, oracle, x, dev)
+    # the same ratios at a scale whose reciprocal is not a power of two times a short number
+    _check(capi, oracle, (x.float() * 0.7431).to(dtype), dev)
+    _check(capi, oracle, (x.float() * 1.0e-3).to(dtype), dev)
+
+
 def test_strided_rows_and_empty(capi, oracle, dev):
     lib = capi.lib()
     x = torch.randn((16, 256), dtype=torch.float32).to(torch.bfloat16)
