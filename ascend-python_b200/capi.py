@@ -18,7 +18,7 @@ LIB_PATH = _PKG / "lib" / "libqmm_b200.so"
 
 QMM_OK = 0
 DTYPE_BF16, DTYPE_F16, DTYPE_F32, DTYPE_I32, DTYPE_NONE = 0, 1, 2, 3, -1
-ALGO_AUTO, ALGO_TILE, ALGO_STREAMK, ALGO_SIMT, ALGO_PAIR = 0, 1, 2, 3, 4
+ALGO_AUTO, ALGO_TILE, ALGO_STREAMK, ALGO_SIMT, ALGO_PAIR, ALGO_SPLITK = 0, 1, 2, 3, 4, 5
 UNIQUE_ID_BYTES = 128
 
 # every symbol include/qmm_b200.h declares

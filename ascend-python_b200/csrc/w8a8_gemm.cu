@@ -91,7 +91,10 @@ template <typename OutT, bool B_MN_MAJOR>
 __global__ void __launch_bounds__(kTileThreads, 1)
 w8a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_out, EpilogueParams ep, int K, int use_tma_store,
-                 uint32_t *status) {
+                 int slices, int slice_rows, uint32_t *status) {
+    // slices > 1: split-K.  Work item w = slice * tiles + tile multiplies the slice's share of the k
+    // blocks and stores raw int32 sums at row slice * slice_rows + m of tmap_out (a scratch array
+    // [slices][slice_rows][N]); a second kernel adds the slices and applies the epilogue.
     // The 128-byte swizzle of TMA and of the MMA descriptors needs 1024-byte aligned tiles.
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t smem_base = smem_u32(smem_raw);
@@ -111,6 +114,8 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int tiles_n = static_cast<int>((ep.N + kBN - 1) / kBN);
     const int num_tiles = tiles_m * tiles_n;
     const int num_kb = (K + kBK - 1) / kBK;
+    const int num_items = num_tiles * slices;
+    const int kb_per_slice = (num_kb + slices - 1) / slices;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -141,10 +146,12 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         // ---------------- TMA producer ----------------
         uint32_t stage = 0, phase = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
             int m_blk, n_blk;
-            tile_coords(tile, tiles_m, tiles_n, m_blk, n_blk);
-            for (int kb = 0; kb < num_kb; ++kb) {
+            tile_coords(item % num_tiles, tiles_m, tiles_n, m_blk, n_blk);
+            const int kb0 = (item / num_tiles) * kb_per_slice;
+            const int kb1 = min(num_kb, kb0 + kb_per_slice);
+            for (int kb = kb0; kb < kb1; ++kb) {
                 ok = mbar_wait(smem_u32(&tail->empty[stage]), phase ^ 1, abort_flag, 1);
                 if (!ok) break;
                 if (lane == 0) {
@@ -186,7 +193,7 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         uint32_t stage = 0, phase = 0;
         int local = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++local) {
             const uint32_t buf = local & 1;
             const uint32_t buf_phase = (local >> 1) & 1;
             ok = mbar_wait(smem_u32(&tail->tmem_empty[buf]), buf_phase ^ 1, abort_flag, 2);
@@ -194,7 +201,9 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + buf * kBN;
             uint32_t accumulate = 0;
-            for (int kb = 0; kb < num_kb; ++kb) {
+            const int kb0 = (item / num_tiles) * kb_per_slice;
+            const int kb1 = min(num_kb, kb0 + kb_per_slice);
+            for (int kb = kb0; kb < kb1; ++kb) {
                 ok = mbar_wait(full0 + stage * 8, phase, abort_flag, 3);
                 if (!ok) break;
                 tc_fence_after();
@@ -223,9 +232,10 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         int local = 0;
         bool ok = true;
         if (lane == 0 && use_tma_store) tma_prefetch_desc(&tmap_out);
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++local) {
             int m_blk, n_blk;
-            tile_coords(tile, tiles_m, tiles_n, m_blk, n_blk);
+            tile_coords(item % num_tiles, tiles_m, tiles_n, m_blk, n_blk);
+            const int slice = item / num_tiles;
             const uint32_t buf = local & 1;
             const uint32_t buf_phase = (local >> 1) & 1;
             ok = mbar_wait(smem_u32(&tail->tmem_full[buf]), buf_phase, abort_flag, 4);
@@ -235,7 +245,8 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBN;
             if (use_tma_store) {
                 epilogue_warp_tile_tma<OutT, kBN>(ep, &tmap_out, taddr, m_warp0, static_cast<int64_t>(n_blk) * kBN,
-                                                  my_stage, my_cols, chunk_counter);
+                                                  my_stage, my_cols, chunk_counter,
+                                                  slices > 1 ? static_cast<int64_t>(slice) * slice_rows + m_warp0 : -1);
             } else {
 #pragma unroll 1
                 for (int c = 0; c < kBN / 32; ++c) {
@@ -365,7 +376,103 @@ int launch_tile(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk
     auto kern = mn_major ? w8a8_tile_kernel<OutT, true> : w8a8_tile_kernel<OutT, false>;
     QMM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(kTileSmemBytes)));
-    kern<<<grid, kTileThreads, kTileSmemBytes, stream>>>(ta, tb, tout, ep, static_cast<int>(K), use_tma_store, status);
+    kern<<<grid, kTileThreads, kTileSmemBytes, stream>>>(ta, tb, tout, ep, static_cast<int>(K), use_tma_store, 1, 0,
+                                                         status);
+    QMM_CUDA_OK(cudaGetLastError());
+    return QMM_OK;
+}
+
+// ---- split-K for shapes whose tiles leave most SMs idle (decode with a narrow N and a long K) ----
+
+// Adds the slices' int32 sums, applies the epilogue and zeroes what it read (the scratch is shared with
+// the stream-K kernel, which relies on finding zeros).
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(int32_t *__restrict__ scratch, int slices, int64_t slice_elems, EpilogueParams ep) {
+    const int64_t vecs = ep.M * ep.N / 4;  // N is a multiple of 4
+    for (int64_t v = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < vecs;
+         v += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        int4 acc = make_int4(0, 0, 0, 0);
+        for (int s = 0; s < slices; ++s) {
+            int4 *src = reinterpret_cast<int4 *>(scratch + s * slice_elems) + v;
+            const int4 a = __ldcg(src);
+            acc.x += a.x;
+            acc.y += a.y;
+            acc.z += a.z;
+            acc.w += a.w;
+            __stcg(src, make_int4(0, 0, 0, 0));
+        }
+        const int64_t e = v * 4;
+        const int64_t m = e / ep.N, n = e - m * ep.N;
+        epilogue_one<OutT>(ep, m, n, acc.x);
+        epilogue_one<OutT>(ep, m, n + 1, acc.y);
+        epilogue_one<OutT>(ep, m, n + 2, acc.z);
+        epilogue_one<OutT>(ep, m, n + 3, acc.w);
+    }
+}
+
+// Slices for a decode shape: enough to occupy the SMs, at least eight k blocks each.
+int splitk_slices(int64_t M, int64_t N, int64_t K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 1;
+    const int64_t tiles = ((M + kBM - 1) / kBM) * ((N + kBN - 1) / kBN);
+    const int64_t num_kb = (K + kBK - 1) / kBK;
+    int64_t s = sm_count() / tiles;
+    if (s > num_kb / 8) s = num_kb / 8;
+    if (s > 8) s = 8;
+    return s < 2 ? 1 : static_cast<int>(s);
+}
+
+size_t splitk_scratch_bytes(int64_t M, int64_t N, int64_t K) {
+    const int s = splitk_slices(M, N, K);
+    if (s < 2 || N % 4 != 0) return 0;
+    return static_cast<size_t>(s) * ((M + kBM - 1) / kBM * kBM) * N * sizeof(int32_t);
+}
+
+template <typename OutT>
+int launch_tile_splitk(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
+                       const EpilogueParams &ep, int64_t K, void *workspace, cudaStream_t stream) {
+    const int slices = splitk_slices(ep.M, ep.N, K);
+    const int64_t slice_rows = (ep.M + kBM - 1) / kBM * kBM;
+    CUtensorMap ta, tb, tout;
+    int rc = make_tmap_2d(&ta, x1, 1, static_cast<uint64_t>(K), static_cast<uint64_t>(ep.M),
+                          static_cast<uint64_t>(ld_x1), kBK, kBM, true);
+    if (rc != QMM_OK) return rc;
+    const bool mn_major = (x2_sn == 1);
+    if (mn_major) {
+        rc = make_tmap_2d(&tb, x2, 1, static_cast<uint64_t>(ep.N), static_cast<uint64_t>(K),
+                          static_cast<uint64_t>(x2_sk), 128, kBK, true);
+    } else {
+        rc = make_tmap_2d(&tb, x2, 1, static_cast<uint64_t>(K), static_cast<uint64_t>(ep.N),
+                          static_cast<uint64_t>(x2_sn), kBK, kBN, true);
+    }
+    if (rc != QMM_OK) return rc;
+    rc = make_tmap_2d(&tout, workspace, 4, static_cast<uint64_t>(ep.N), static_cast<uint64_t>(slices * slice_rows),
+                      static_cast<uint64_t>(ep.N), 32, 32, true);
+    if (rc != QMM_OK) return rc;
+    EpilogueParams raw;  // first pass: raw int32 sums, no scale, no bias
+    raw.scale = nullptr;
+    raw.pertoken_scale = nullptr;
+    raw.bias = nullptr;
+    raw.bias_dtype = QMM_DTYPE_NONE;
+    raw.scale_is_scalar = 1;
+    raw.out = workspace;
+    raw.ld_out = ep.N;
+    raw.M = ep.M;
+    raw.N = ep.N;
+    const int items = static_cast<int>(((ep.M + kBM - 1) / kBM) * ((ep.N + kBN - 1) / kBN)) * slices;
+    int ctas = sm_count() - g_sm_reserve;
+    if (ctas < 1) ctas = 1;
+    const int grid = items < ctas ? items : ctas;
+    auto kern = mn_major ? w8a8_tile_kernel<int32_t, true> : w8a8_tile_kernel<int32_t, false>;
+    QMM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(kTileSmemBytes)));
+    kern<<<grid, kTileThreads, kTileSmemBytes, stream>>>(ta, tb, tout, raw, static_cast<int>(K), 1, slices,
+                                                         static_cast<int>(slice_rows), device_status_word());
+    QMM_CUDA_OK(cudaGetLastError());
+    const int64_t vecs = ep.M * ep.N / 4;
+    const int rgrid = static_cast<int>(vecs / 256 + 1 < 4 * sm_count() ? vecs / 256 + 1 : 4 * sm_count());
+    splitk_reduce_kernel<OutT><<<rgrid, 256, 0, stream>>>(static_cast<int32_t *>(workspace), slices,
+                                                          slice_rows * ep.N, ep);
     QMM_CUDA_OK(cudaGetLastError());
     return QMM_OK;
 }
@@ -418,6 +525,10 @@ int quant_matmul_dispatch(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int
     if (algo == QMM_ALGO_AUTO) {
         if (!tma_ok)
             algo = QMM_ALGO_SIMT;
+        else if (ep.M > 16 && ep.M <= 128 && workspace != nullptr && splitk_scratch_bytes(ep.M, ep.N, K) > 0 &&
+                 workspace_bytes >= splitk_scratch_bytes(ep.M, ep.N, K) &&
+                 (reinterpret_cast<uintptr_t>(workspace) & 15) == 0)
+            algo = QMM_ALGO_TCGEN05_SPLITK;  // few tiles, long K: the slices fill the SMs
         else if (streamk_supported(ep.M, ep.N, K, x2_sn) && workspace != nullptr &&
                  workspace_bytes >= streamk_workspace_bytes(ep.M, ep.N, K) && prefer_streamk(ep.M, ep.N))
             algo = QMM_ALGO_TCGEN05_STREAMK;
@@ -426,7 +537,8 @@ int quant_matmul_dispatch(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int
         else
             algo = QMM_ALGO_TCGEN05_TILE;
     }
-    if ((algo == QMM_ALGO_TCGEN05_TILE || algo == QMM_ALGO_TCGEN05_STREAMK || algo == QMM_ALGO_TCGEN05_PAIR) && !tma_ok)
+    if ((algo == QMM_ALGO_TCGEN05_TILE || algo == QMM_ALGO_TCGEN05_STREAMK || algo == QMM_ALGO_TCGEN05_PAIR ||
+         algo == QMM_ALGO_TCGEN05_SPLITK) && !tma_ok)
         return fail(QMM_ERR_UNSUPPORTED,
                     "qmm_quant_matmul: tcgen05 kernels need 16-byte aligned operands and row pitches");
     switch (algo) {
@@ -441,6 +553,21 @@ int quant_matmul_dispatch(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int
             }
         case QMM_ALGO_TCGEN05_PAIR:
             return launch_pair(x1, ld_x1, x2, x2_sk, x2_sn, ep, out_dtype, K, stream);
+        case QMM_ALGO_TCGEN05_SPLITK:
+            if (workspace == nullptr || splitk_scratch_bytes(ep.M, ep.N, K) == 0 ||
+                workspace_bytes < splitk_scratch_bytes(ep.M, ep.N, K) ||
+                (reinterpret_cast<uintptr_t>(workspace) & 15) != 0)
+                return fail(QMM_ERR_UNSUPPORTED,
+                            "qmm_quant_matmul: split-K needs at least two slices of eight k blocks, N a multiple of "
+                            "4 and the scratch qmm_quant_matmul_workspace_size reports");
+            switch (out_dtype) {
+                case QMM_DTYPE_BF16:
+                    return launch_tile_splitk<__nv_bfloat16>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, workspace, stream);
+                case QMM_DTYPE_F16:
+                    return launch_tile_splitk<__half>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, workspace, stream);
+                default:
+                    return launch_tile_splitk<int32_t>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, workspace, stream);
+            }
         case QMM_ALGO_TCGEN05_STREAMK:
             return launch_streamk(x1, ld_x1, x2, x2_sk, x2_sn, ep, out_dtype, K, workspace, workspace_bytes, stream);
         case QMM_ALGO_SIMT:
@@ -495,6 +622,10 @@ extern "C" int qmm_quant_matmul_workspace_size(int64_t M, int64_t N, int64_t K, 
     *bytes = 0;
     if ((algo == QMM_ALGO_AUTO || algo == QMM_ALGO_TCGEN05_STREAMK) && streamk_supported(M, N, K, 1))
         *bytes = streamk_workspace_bytes(M, N, K);
+    if ((algo == QMM_ALGO_AUTO || algo == QMM_ALGO_TCGEN05_SPLITK) && M <= 128) {
+        const size_t sk = splitk_scratch_bytes(M, N, K);
+        if (sk > *bytes) *bytes = sk;
+    }
     return QMM_OK;
 }
 

@@ -58,7 +58,8 @@ enum {
     QMM_ALGO_TCGEN05_TILE = 1,   /* 128x256 output tiles, one CTA per tile (prefill) */
     QMM_ALGO_TCGEN05_STREAMK = 2, /* weights as the MMA's M operand, K split over CTAs (decode) */
     QMM_ALGO_SIMT = 3,           /* dp4a kernel: any alignment, any stride */
-    QMM_ALGO_TCGEN05_PAIR = 4    /* 256x256 output tiles on CTA pairs, cta_group::2 MMA (prefill) */
+    QMM_ALGO_TCGEN05_PAIR = 4,   /* 256x256 output tiles on CTA pairs, cta_group::2 MMA (prefill) */
+    QMM_ALGO_TCGEN05_SPLITK = 5  /* the one-CTA tile kernel over K slices + a reduce kernel (M <= 128, few tiles) */
 };
 
 /* Text of the last error raised on the calling thread ("" if none). */

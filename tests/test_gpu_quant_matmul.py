@@ -142,6 +142,21 @@ def test_streamk_scratch_is_left_clean(capi, oracle, dev):
     assert checked >= 1
 
 
+@pytest.mark.parametrize("transposed", [False, True])
+@pytest.mark.parametrize("shape", [(17, 2048, 256), (32, 8192, 2048), (100, 4096, 1008), (128, 28672, 512)])
+def test_splitk(capi, oracle, dev, shape, transposed):
+    """Few output tiles, long K: the tile kernel over K slices + the reduce kernel.  Integer sums are
+    order-independent, so the result is the oracle's bit for bit; the scratch is zero afterwards."""
+    M, K, N = shape
+    a, w, scale, pt, bias = _make(oracle, M, K, N, seed=M + N)
+    _compare(capi, oracle, dev, a, w, scale, pt, bias, torch.bfloat16, capi.ALGO_SPLITK, transposed)
+    _compare(capi, oracle, dev, a, w, scale, None, bias.to(torch.float16), torch.float16, capi.ALGO_SPLITK, transposed)
+    torch.cuda.synchronize()
+    for key, ws in capi._workspaces.items():
+        if key[0] == "w8a8":
+            assert int(ws.count_nonzero().item()) == 0
+
+
 def _checksums(a_dev, w_dev, acc_dev):
     """Checksum of checksums: column sums and row sums of the int32 result against
     (sum of rows of x1) @ x2 and x1 @ (sum of columns of x2), all in exact integer arithmetic."""
