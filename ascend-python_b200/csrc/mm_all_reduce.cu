@@ -424,6 +424,11 @@ extern "C" int qmm_mm_all_reduce(const int8_t *x1, int64_t ld_x1, const int8_t *
             pp.N = N;
             pp.rows_per = chunks == 1 ? rows_per_full : (rows + c.nranks - 1) / c.nranks;
             pp.pushed = 0;
+            {
+                const size_t own_bytes = static_cast<size_t>(pp.rows_per) * N * elt;
+                size_t n = (own_bytes + kPeerChunkBytes - 1) / kPeerChunkBytes;
+                pp.nchunks = static_cast<int>(n < 1 ? 1 : (n > kPeerChunks ? kPeerChunks : n));
+            }
             pp.partial_off = kPeerFlagBytes + row_bytes0;
             pp.red_off = red_area + row_bytes0;
             pp.out = static_cast<uint8_t *>(out) + row_bytes0;
@@ -459,8 +464,8 @@ extern "C" int qmm_mm_all_reduce(const int8_t *x1, int64_t ld_x1, const int8_t *
                 QMM_CUDA_OK(cudaStreamWaitEvent(c.stream, c.chunk_ready[ci], 0));
                 ks = c.stream;
             }
-            // every CTA must be resident (ranks wait on one another's CTAs): one or two per SM
-            const int grid = sm_count() * (chunks > 1 ? 1 : 2);
+            // every CTA must be resident (ranks wait on one another's CTAs): one per SM
+            const int grid = sm_count();
             const bool mc = pp.mc_base != nullptr;
             if (out_dtype == QMM_DTYPE_BF16) {
                 if (mc)

@@ -23,7 +23,7 @@
 // the rank's own region: each byte then crosses a link once per direction instead of twice.
 //
 // The kernels of different ranks wait on one another only across GPUs; within a GPU no CTA waits on
-// another CTA, and the grid is at most one CTA per SM, so every CTA is resident.  Every wait is
+// another CTA, and the grid is one CTA per SM, so every CTA is resident.  Every wait is
 // bounded (2 s): on expiry the kernel records a status code and leaves without touching peer data
 // again.  Flags carry the call's epoch, which only grows, so they are never reset.
 //
@@ -38,7 +38,9 @@
 namespace qmm {
 
 constexpr int kPeerMaxRanks = 8;
-constexpr int kPeerChunks = 592;                  // reduce/gather granularity (2 or 4 per CTA on 148 SMs)
+constexpr int kPeerChunks = 592;                  // most chunks a rank's rows are cut into (size of a flag row)
+constexpr size_t kPeerChunkBytes = 64 * 1024;     // aimed-at chunk size: enough loads in flight per CTA to hide
+                                                  // the NVLink round trip, few enough flag operations
 constexpr size_t kPeerFlagBytes = 64 * 1024;      // flag A: [W] at 0; flag B: [W][kPeerChunks] at 1 KiB
 constexpr size_t kPeerFlagBOffset = 1024;
 constexpr int kPeerThreads = 512;
@@ -51,6 +53,7 @@ struct PeerParams {
     uint32_t epoch;
     int64_t M, N;
     int64_t rows_per;              // rows owned by a rank (the last owner may hold fewer)
+    int nchunks;                   // chunks a rank's rows are cut into (<= kPeerChunks)
     int pushed;                    // the matmul already delivered every rank's share of the rows this rank owns
                                    // into this rank's region: [source rank][rows_per][N] in the partial area
     size_t partial_off, red_off;   // byte offsets of the two data areas inside a region
@@ -68,13 +71,17 @@ __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
 }
 
 // Waits until *flag has reached `epoch` (epochs only grow; the difference is taken modulo 2^32).
+// The poll backs off with nanosleep: hundreds of CTAs polling at full speed (system-scope loads, plus
+// reads of the host-mapped status word) were measured to slow the very transfers they wait for by
+// several times.
 __device__ __noinline__ bool peer_wait_flag(const uint32_t *flag, uint32_t epoch, uint32_t *status, uint32_t where) {
     if (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) >= 0) return true;
     const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
     while (true) {
+        __nanosleep(spins < 16 ? 100 : 400);
         if (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) >= 0) return true;
-        if (((++spins) & 0x3fu) == 0) {
+        if (((++spins) & 0xfffu) == 0) {  // every millisecond or two
             if (status != nullptr && *reinterpret_cast<volatile uint32_t *>(status) != 0) return false;
             if (globaltimer_ns() - t0 > kWaitLimitNs) {
                 if (status != nullptr) atomicMax(status, DEV_STATUS_PEER_TIMEOUT | where);
@@ -120,14 +127,57 @@ __device__ __forceinline__ void accumulate8(const uint4 &v, float (&acc)[8]) {
 }
 
 // vectors (16 bytes = 8 elements) of chunk c of a range of `total` vectors
-__device__ __forceinline__ void chunk_bounds(int64_t total, int c, int64_t &lo, int64_t &hi) {
-    lo = total * c / kPeerChunks;
-    hi = total * (c + 1) / kPeerChunks;
+__device__ __forceinline__ void chunk_bounds(int64_t total, int c, int nchunks, int64_t &lo, int64_t &hi) {
+    lo = total * c / nchunks;
+    hi = total * (c + 1) / nchunks;
+}
+
+// Sum of the ranks' shares of the vectors [lo, hi) of this rank's rows, in rank order; WW: ranks rounded
+// up (2, 4, 8), U: vectors per thread and pass.
+template <typename T, bool MC, int WW, int U>
+__device__ __forceinline__ void reduce_chunk(const PeerParams &p, int64_t lo, int64_t hi, size_t own_byte0, uint4 *red,
+                                             uint4 *out_own) {
+    const int W = p.world;
+    for (int64_t v0 = lo + threadIdx.x; v0 < hi; v0 += U * kPeerThreads) {
+        uint4 part[U][WW];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int r = 0; r < WW; ++r)
+                if (r < W && v0 + u * kPeerThreads < hi) {
+                    const uint8_t *src = p.pushed ? p.base[p.rank] + p.partial_off +
+                                                        static_cast<size_t>(r) * p.rows_per * p.N * sizeof(T)
+                                                  : p.base[r] + p.partial_off + own_byte0;
+                    part[u][r] = __ldcg(reinterpret_cast<const uint4 *>(src) + v0 + u * kPeerThreads);
+                }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t v = v0 + u * kPeerThreads;
+            if (v < hi) {
+                float acc[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+#pragma unroll
+                for (int r = 0; r < WW; ++r)
+                    if (r < W) accumulate8<T>(part[u][r], acc);
+                uint4 o;
+                o.x = pack2<T>(acc[0], acc[1]);
+                o.y = pack2<T>(acc[2], acc[3]);
+                o.z = pack2<T>(acc[4], acc[5]);
+                o.w = pack2<T>(acc[6], acc[7]);
+                if constexpr (MC)
+                    multimem_st(p.mc_base + p.red_off + own_byte0 + v * 16, o);
+                else
+                    red[v] = o;
+                out_own[v] = o;
+            }
+        }
+    }
 }
 
 // MC: the regions have a multicast mapping (p.mc_base)
 template <typename T, bool MC>
-__global__ void __launch_bounds__(kPeerThreads, 2) peer_all_reduce_kernel(PeerParams p) {
+__global__ void __launch_bounds__(kPeerThreads, 1) peer_all_reduce_kernel(PeerParams p) {
     __shared__ int s_ok;
     const int W = p.world;
     uint32_t *my_flags = reinterpret_cast<uint32_t *>(p.base[p.rank]);
@@ -153,9 +203,9 @@ __global__ void __launch_bounds__(kPeerThreads, 2) peer_all_reduce_kernel(PeerPa
     const size_t own_byte0 = static_cast<size_t>(r0) * p.N * sizeof(T);
     uint4 *red = reinterpret_cast<uint4 *>(p.base[p.rank] + p.red_off + own_byte0);
     uint4 *out_own = reinterpret_cast<uint4 *>(static_cast<uint8_t *>(p.out) + own_byte0);
-    for (int c = blockIdx.x; c < kPeerChunks; c += gridDim.x) {
+    for (int c = blockIdx.x; c < p.nchunks; c += gridDim.x) {
         int64_t lo, hi;
-        chunk_bounds(own_vecs, c, lo, hi);
+        chunk_bounds(own_vecs, c, p.nchunks, lo, hi);
         if (MC && !p.pushed) {
             const uint8_t *mc_part = p.mc_base + p.partial_off + own_byte0;
             uint8_t *mc_red = p.mc_base + p.red_off + own_byte0;
@@ -173,33 +223,13 @@ __global__ void __launch_bounds__(kPeerThreads, 2) peer_all_reduce_kernel(PeerPa
                     }
             }
         } else {
-            for (int64_t v = lo + threadIdx.x; v < hi; v += kPeerThreads) {
-                uint4 part[kPeerMaxRanks];  // all ranks' loads of a vector are in flight together
-#pragma unroll
-                for (int r = 0; r < kPeerMaxRanks; ++r)
-                    if (r < W) {
-                        const uint8_t *src = p.pushed ? p.base[p.rank] + p.partial_off +
-                                                            static_cast<size_t>(r) * p.rows_per * p.N * sizeof(T)
-                                                      : p.base[r] + p.partial_off + own_byte0;
-                        part[r] = __ldcg(reinterpret_cast<const uint4 *>(src) + v);
-                    }
-                float acc[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
-#pragma unroll
-                for (int r = 0; r < kPeerMaxRanks; ++r)
-                    if (r < W) accumulate8<T>(part[r], acc);
-                uint4 o;
-                o.x = pack2<T>(acc[0], acc[1]);
-                o.y = pack2<T>(acc[2], acc[3]);
-                o.z = pack2<T>(acc[4], acc[5]);
-                o.w = pack2<T>(acc[6], acc[7]);
-                if constexpr (MC)
-                    multimem_st(p.mc_base + p.red_off + own_byte0 + v * 16, o);
-                else
-                    red[v] = o;
-                out_own[v] = o;
-            }
+            // eight 16-byte loads per thread are in flight: U vectors x W ranks
+            if (W <= 2)
+                reduce_chunk<T, MC, 2, 4>(p, lo, hi, own_byte0, red, out_own);
+            else if (W <= 4)
+                reduce_chunk<T, MC, 4, 2>(p, lo, hi, own_byte0, red, out_own);
+            else
+                reduce_chunk<T, MC, 8, 1>(p, lo, hi, own_byte0, red, out_own);
         }
         __syncthreads();
         if (threadIdx.x < W && static_cast<int>(threadIdx.x) != p.rank) {
@@ -211,15 +241,16 @@ __global__ void __launch_bounds__(kPeerThreads, 2) peer_all_reduce_kernel(PeerPa
 
     // ---- 3. gather the other ranks' rows as they become ready ----
     const uint32_t *my_b = reinterpret_cast<const uint32_t *>(p.base[p.rank] + kPeerFlagBOffset);
-    const int items = (W - 1) * kPeerChunks;
+    const int items = (W - 1) * p.nchunks;
     for (int i = blockIdx.x; i < items; i += gridDim.x) {
-        const int src = (p.rank + 1 + i / kPeerChunks) % W;  // start with the next rank so that sources differ
-        const int c = i % kPeerChunks;
+        // consecutive CTAs read from different ranks, every rank starting with its right-hand neighbour
+        const int src = (p.rank + 1 + i % (W - 1)) % W;
+        const int c = i / (W - 1);
         const int64_t s0 = static_cast<int64_t>(src) * p.rows_per;
         const int64_t s1 = (s0 + p.rows_per < p.M) ? s0 + p.rows_per : p.M;
         const int64_t src_vecs = (s1 > s0 ? (s1 - s0) : 0) * vec_per_row;
         int64_t lo, hi;
-        chunk_bounds(src_vecs, c, lo, hi);
+        chunk_bounds(src_vecs, c, p.nchunks, lo, hi);
         __syncthreads();  // s_ok of the previous item has been read by everyone
         if (threadIdx.x == 0)
             s_ok = peer_wait_flag(my_b + static_cast<size_t>(src) * kPeerChunks + c, p.epoch, p.status, 0x02) ? 1 : 0;

@@ -112,13 +112,16 @@ def _ensure_peer_memory(name: str, M: int, N: int, device) -> None:
     The regions come from torch's symmetric memory (one allocation per rank, mapped by all ranks of
     the node); the library then reduces and gathers through NVLink loads instead of NCCL.  The first
     call, and any call that needs a larger region, is collective: all ranks reach it with the same
-    M and N.  Where symmetric memory is not available the communicator silently stays on NCCL.
-    QMM_ALLREDUCE=nccl disables the path.
+    M and N.  Where symmetric memory is not available the communicator stays on NCCL.
+    QMM_ALLREDUCE = nccl | p2p | multimem forces a path; unset, peer memory with plain peer loads is used
+    (measured on B200, M=4096, N=8192: 381 us against 424 us with NCCL on two GPUs, 250 us against 356 us on
+    eight; in-switch reduction measured the same as plain loads, which keep the rank-order sum).
     """
     import os
 
     info = _comm_names.get(name)
-    if not isinstance(info, dict) or os.environ.get("QMM_ALLREDUCE", "") == "nccl":
+    mode = os.environ.get("QMM_ALLREDUCE", "")
+    if not isinstance(info, dict) or mode == "nccl":
         return
     world = info["world"]
     if world < 2 or world > 8:
@@ -145,12 +148,8 @@ def _ensure_peer_memory(name: str, M: int, N: int, device) -> None:
         torch.cuda.synchronize(device)
         dist.barrier(group=info["group"])  # every region is zero before anyone raises a flag in it
         ptrs = (ctypes.c_void_p * world)(*[int(a) for a in handle.buffer_ptrs])
-        # In-switch reduction pays from four ranks on (with two, every byte would cross the switch and
-        # come back); QMM_ALLREDUCE=multimem / p2p force one or the other.
-        mode = os.environ.get("QMM_ALLREDUCE", "")
-        mc = int(getattr(handle, "multicast_ptr", 0) or 0)
-        if mode == "p2p" or (mode != "multimem" and world < 4):
-            mc = 0
+        # plain peer loads unless in-switch reduction is asked for
+        mc = int(getattr(handle, "multicast_ptr", 0) or 0) if mode == "multimem" else 0
         _capi.check(lib.qmm_comm_attach_peer_memory(name.encode(), ptrs, ctypes.c_void_p(mc or None), nbytes),
                     "qmm_comm_attach_peer_memory")
         _peer_memory[name] = dict(bytes=nbytes, tensor=buf, handle=handle)

@@ -74,12 +74,11 @@ def _rank_main(rank, world, port, shapes, c2p):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,path", [(2, "peer"), (2, "multimem"), (2, "nccl"), (4, "peer"), (8, "peer"), (8, "p2p")])
+@pytest.mark.parametrize("world,path", [(2, "peer"), (2, "multimem"), (2, "nccl"), (4, "peer"), (4, "multimem"), (8, "peer"), (8, "multimem")])
 def test_multi_rank(oracle, pkg, world, path):
-    """path "peer": calls with comm_turn == 0 reduce and gather through peer memory in the library's own
-    kernel (the default where symmetric memory is available; with in-switch reduction where the regions have
-    an NVLink multicast mapping and there are at least four ranks); "p2p" / "multimem" force plain peer loads /
-    in-switch reduction; "nccl" forces NCCL for every call."""
+    """path "peer": the default (calls with comm_turn == 0 reduce and gather through peer memory in the
+    library's own kernel, plain peer loads); "multimem": the same with in-switch reduction / broadcast;
+    "nccl" forces NCCL for every call."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
