@@ -28,9 +28,10 @@
 // again.  Flags carry the call's epoch, which only grows, so they are never reset.
 //
 // Buffer reuse across calls needs no extra synchronisation: a rank finishes step 3 only after all
-// peers have raised all their B flags, i.e. after they have read its partial; and it overwrites its
-// reduced rows in the next call only after all peers have raised the next A flag, i.e. after their
-// previous kernel, which read those rows, has ended.
+// peers have raised all their B flags, i.e. after they are done reading partials (its own, or - with
+// pushed tiles - the area its next matmul will write into); and it overwrites its reduced rows in
+// the next call only after all peers have raised the next A flag, i.e. after their previous kernel,
+// which read those rows, has ended.
 #pragma once
 
 #include "qmm_common.cuh"

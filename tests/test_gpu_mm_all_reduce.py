@@ -84,8 +84,9 @@ def test_multi_rank(oracle, pkg, world, path):
     import torch.multiprocessing as mp
     from ascend_python_b200.sharding import shard_row_parallel
 
+    # the last shape needs larger peer regions than the first ones allocated: the regions are re-made
     shapes = [(256, 1024, 512, 0), (2048, 4096, 1024, 2), (1000, 2048, 768, 3), (1000, 2048, 768, 0),
-              (2048, 4096, 1024, 0), (3, 512, 264, 0)]
+              (2048, 4096, 1024, 0), (3, 512, 264, 0), (4096, 512, 4352, 0)]
     ctx = mp.get_context("spawn")
     c2p = ctx.Queue()
     port = 29700 + os.getpid() % 1000
