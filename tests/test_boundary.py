@@ -46,6 +46,17 @@ def test_validation_needs_no_gpu(capi):
     rc = lib.qmm_mm_all_reduce(None, 8, None, 8, 1, None, 8, None, None, -1, None, 0, 8, 4, 8, 8, b"c", b"max", 0,
                                None, 0, None)
     assert rc == 1 and b"reduce_op" in lib.qmm_last_error()
+    # peer memory of the allreduce: the size is plain arithmetic (64 KiB of flags, the partials as
+    # [ranks][rows per rank rounded up to 32][N], the reduced [M][N], 16-bit elements, 256-byte rounding)
+    need = ctypes.c_size_t(0)
+    assert lib.qmm_comm_peer_memory_size(4096, 8192, 8, ctypes.byref(need)) == 0
+    assert need.value == 65536 + 2 * 4096 * 8192 * 2
+    assert lib.qmm_comm_peer_memory_size(1000, 768, 3, ctypes.byref(need)) == 0
+    assert need.value == 65536 + 3 * 352 * 768 * 2 + 1000 * 768 * 2
+    assert lib.qmm_comm_peer_memory_size(-1, 8, 2, ctypes.byref(need)) == 1
+    regions = (ctypes.c_void_p * 2)(None, None)
+    rc = lib.qmm_comm_attach_peer_memory(b"no-such-comm", regions, None, 1 << 20)
+    assert rc == 5 and b"not registered" in lib.qmm_last_error()
 
 
 def test_missing_library_fails_loudly(capi, monkeypatch):
