@@ -45,6 +45,43 @@ def test_single_rank_communicator(capi, oracle, dev):
     assert lib.qmm_comm_destroy(b"solo") == 5  # not found any more
 
 
+def test_missing_rank_times_out(capi, oracle, dev):
+    """Failure detection without a fault: a two-rank communicator whose other rank never arrives.  Both
+    regions are ordinary buffers of this GPU, nothing ever raises rank 1's "partial complete" flag, so the
+    reduce kernel's bounded wait runs out (2 s), it records a status code and returns; the context stays
+    usable and the next call of another operator is correct."""
+    sys.path.insert(0, str(PKG_DIR))
+    try:
+        import torch_npu
+    finally:
+        sys.path.pop(0)
+    lib = capi.lib()
+    M, K, N = 256, 512, 512
+    # adopted as a communicator handle but never used: the peer-memory path makes no NCCL call
+    placeholder = ctypes.c_void_p(1)
+    capi.check(lib.qmm_comm_register(b"half", placeholder, 2, 0), "qmm_comm_register")
+    try:
+        need = ctypes.c_size_t(0)
+        capi.check(lib.qmm_comm_peer_memory_size(M, N, 2, ctypes.byref(need)), "qmm_comm_peer_memory_size")
+        regions = [torch.zeros(need.value, dtype=torch.uint8, device=dev) for _ in range(2)]
+        ptrs = (ctypes.c_void_p * 2)(*[r.data_ptr() for r in regions])
+        capi.check(lib.qmm_comm_attach_peer_memory(b"half", ptrs, None, need.value), "qmm_comm_attach_peer_memory")
+        x, w, scale, bias = oracle.make_w8a8_inputs(M, K, N, seed=77)
+        q, s = torch_npu.npu_dynamic_quant(x.to(dev))
+        torch_npu.npu_mm_all_reduce_base(q, w.to(dev), "half", reduce_op="sum", dequant_scale=scale.to(dev),
+                                         pertoken_scale=s)
+        torch.cuda.synchronize()  # returns after the wait limit, not never
+        status = capi.device_status(reset=True)
+        assert status & 0xffff0000 == 0x30000, f"expected the peer-wait timeout code, got {status:#x}"
+        # the context is intact: a plain matmul right after is bit-exact
+        q_ref, s_ref = oracle.dynamic_quant(x)
+        acc_ref = oracle.quant_matmul(q_ref, w, scale, output_dtype=torch.int32)
+        acc = capi.quant_matmul(q, w.to(dev), None, output_dtype=torch.int32)
+        assert torch.equal(acc.cpu(), acc_ref)
+    finally:
+        capi.check(lib.qmm_comm_destroy(b"half"), "qmm_comm_destroy")
+
+
 def _rank_main(rank, world, port, shapes, c2p):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
