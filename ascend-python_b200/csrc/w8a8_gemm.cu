@@ -489,10 +489,12 @@ int launch_simt(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk
 }
 
 // Decode shapes (M <= 128): stream-K keeps every SM streaming weights whatever N is, but its split
-// tiles pay for the int32 scratch traffic, which grows with M.  Measured on B200 (K x N = 8192 x 28672
-// and 28672 x 8192): up to 16 tokens stream-K wins everywhere; beyond that the one-CTA tile kernel is
-// ahead as soon as its 128 x 256 tiles occupy most SMs (52 us against 65 us at M = 32, 54 us against
-// 117 us at M = 128 for N = 28672), and for narrow N from about 64 tokens on.
+// tiles pay for the int32 scratch traffic, which grows with M.  Measured on B200 (graph replay):
+// K x N = 8192 x 28672: M = 1 stream-K 46.9 us, tile kernel 54.2 us; M = 8 49.8 / 52.8 us; M = 32
+// 59 / 44 us; M = 128 110 / 46 us.  So up to 16 tokens stream-K wins everywhere; beyond that the
+// one-CTA tile kernel is ahead as soon as its 128 x 256 tiles occupy most SMs.  Shapes with few tiles
+// and a long K (28672 x 8192) go to the tile kernel over K slices before this function is asked
+// (M = 32 47 us, M = 128 61 us against 59 / 85 us for the better of the other two).
 bool prefer_streamk(int64_t M, int64_t N) {
     if (M <= 16) return true;
     const int64_t tiles = (N + kBN - 1) / kBN;
