@@ -9,11 +9,16 @@
 // Numerics (bit-exact contract with the CPU oracle):
 //   scale = amax / 127            IEEE fp32 division
 //   q     = rint(x / scale)       IEEE fp32 division, round half to even
-// The division x / scale runs on the FMA pipe: with y = RN(1/scale), q0 = RN(x*y), the exact
-// remainder r = fma(-q0, scale, x) and q1 = RN(q0 + r*y), q1 is the correctly rounded quotient
-// (Markstein's theorem: y correctly rounded, q0 within one ulp, no underflow, and the significand
-// of the divisor not all ones).  Rows whose scale breaks a precondition take true divisions.
-// bf16/f16 inputs make EXACT ties (x / scale = n + 1/2) common - x and amax are short-mantissa
+// The division x / scale runs on the FMA pipe: with y = RN(1/scale), q0 = RN(x*y) (within two ulps
+// of the quotient), r = fma(-q0, scale, x) (the remainder, one rounding at most) and
+// q1 = RN(q0 + r*y).  q0 + r*y differs from the exact quotient by less than 2^-21 ulp, so q1 is the
+// IEEE quotient unless x/scale lies that close to a rounding boundary without being on it; the
+// integer rint(q1) could differ from rint(x/scale) only if, in addition, that boundary neighbours a
+// half-integer.  The tests compare against IEEE division for every pair of bf16 significands and of
+// f16 significands (quotient significands do not depend on exponents), which covers the inputs this
+// operator accepts.  Rows whose scale is tiny, not finite, or has an all-ones significand take
+// true divisions.
+// bf16/f16 inputs make EXACT ties (x / scale = n + 1/2) common - x and amax are short-significand
 // numbers - so a scheme that falls back to a division near ties would fall back all the time.
 #include "qmm_common.cuh"
 
@@ -158,7 +163,7 @@ dynamic_quant_vec_kernel(const T *__restrict__ x, int64_t rows, int cols, int64_
                 for (int j = 0; j < 8; ++j) {
                     const float q0 = f[j] * rq.inv;
                     const float rem = fmaf(-q0, rq.scale, f[j]);
-                    const float q1 = fmaf(rem, rq.inv, q0);  // = RN(f / scale)
+                    const float q1 = fmaf(rem, rq.inv, q0);  // the IEEE quotient f / scale (see the file header)
                     b[j] = __float_as_uint(q1 + kMagic);
                 }
                 // the int8 results are the low bytes of the biased floats: gather (b0..b3) and (b4..b7)

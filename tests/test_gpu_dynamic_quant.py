@@ -74,6 +74,20 @@ def test_every_mantissa_against_every_maximum(capi, oracle, dev, dtype):
     _check(capi, oracle, (x.float() * 1.0e-3).to(dtype), dev)
 
 
+def test_every_f16_significand_pair(capi, oracle, dev):
+    """All 1024 f16 significands as the row maximum against all 1024 significands of x at eight exponents and
+    both signs: with the quotient's significand independent of the exponents, this is every case the f16
+    path can meet.  16.8 M elements, bit-exact against IEEE division."""
+    mant = torch.arange(1024, 2048, dtype=torch.float32)                      # significands 1.0 .. 2 - 2^-10
+    exps = torch.tensor([2.0 ** -e for e in range(9, 17)])
+    vals = (mant[None, :] * exps[:, None]).reshape(-1)                         # 8192 values in (0, 4)
+    vals = torch.cat([vals, -vals])                                            # 16384 columns
+    amax = (mant / 512.0)[:, None]                                             # 1024 row maxima in [2, 4)
+    x = torch.minimum(torch.maximum(vals[None, :], -amax), amax)
+    x[:, 0] = amax[:, 0]
+    _check(capi, oracle, x.to(torch.float16), dev)
+
+
 def test_strided_rows_and_empty(capi, oracle, dev):
     lib = capi.lib()
     x = torch.randn((16, 256), dtype=torch.float32).to(torch.bfloat16)

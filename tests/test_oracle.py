@@ -54,6 +54,57 @@ def test_dynamic_quant_division_not_reciprocal(oracle):
     assert np.abs(q.numpy().astype(np.int32) - q_recip.astype(np.int32)).max() <= 1
 
 
+def _round_f32(fr):
+    """Fraction -> nearest float32 (ties to even), exactly."""
+    from fractions import Fraction
+
+    if fr == 0:
+        return np.float32(0.0)
+    sign = -1 if fr < 0 else 1
+    a = abs(fr)
+    e = a.numerator.bit_length() - a.denominator.bit_length()
+    if Fraction(2) ** e > a:
+        e -= 1
+    if e < -126:
+        e = -126  # subnormal range: fixed exponent
+    scaled = a / Fraction(2) ** (e - 23)  # integer significand with 24 bits when normal
+    n = scaled.numerator // scaled.denominator
+    rem = scaled - n
+    if rem > Fraction(1, 2) or (rem == Fraction(1, 2) and n % 2 == 1):
+        n += 1
+    return np.float32(sign * float(Fraction(n) * Fraction(2) ** (e - 23)))
+
+
+def test_fma_division_equals_ieee_division():
+    """The division the dynamic-quant kernel runs on the FMA pipe: y = RN(1/s), q0 = RN(x*y),
+    r = RN(x - q0*s) (one fma), q1 = RN(q0 + r*y) (one fma).  q0 is within two ulps of x/s, r carries at most
+    one rounding, so q0 + r*y differs from the exact quotient by less than 2^-21 ulp and q1 = RN(x/s) unless the
+    quotient sits that close to a rounding boundary without being on it.  Checked here with exact rational
+    arithmetic on the operands the kernel sees (s = amax/127 of a 16-bit-float row, |x| <= amax, exact and near
+    ties x/s = n + 1/2 included); the GPU tests run every pair of bf16 / f16 significands."""
+    from fractions import Fraction
+
+    rng = np.random.default_rng(7)
+    checked = 0
+    for _ in range(60):
+        amax = np.float32(torch.tensor(abs(rng.normal()) * 3 + 0.5).to(torch.bfloat16).float().item())
+        s = np.float32(amax) / np.float32(127.0)
+        if (s.view(np.uint32) & 0x7FFFFF) == 0x7FFFFF:
+            continue  # the kernel takes true divisions for an all-ones significand
+        y = np.float32(1.0) / s
+        xs = torch.tensor(rng.uniform(-1, 1, 48) * float(amax)).to(torch.bfloat16).float().numpy()
+        # plus values that make exact or near ties: (n + 1/2) * s rounded to bf16
+        n = rng.integers(-126, 126, 16).astype(np.float32)
+        ties = torch.tensor((n + 0.5) * s).to(torch.bfloat16).float().numpy()
+        for x in np.concatenate([xs, ties]).astype(np.float32):
+            q0 = np.float32(x * y)
+            r = _round_f32(Fraction(float(x)) - Fraction(float(q0)) * Fraction(float(s)))
+            q1 = _round_f32(Fraction(float(q0)) + Fraction(float(r)) * Fraction(float(y)))
+            assert q1 == np.float32(x) / s, (x, s)
+            checked += 1
+    assert checked > 3000
+
+
 def test_quant_matmul_hand_checked(oracle):
     x1 = torch.tensor([[1, -2, 3], [127, 127, 127]], dtype=torch.int8)
     x2 = torch.tensor([[1, 0], [0, 1], [-1, 127]], dtype=torch.int8)
