@@ -13,7 +13,10 @@ N > 1  workload "w8a8_row_parallel_allreduce": M = 4096, K = 28672 sharded evenl
 `value` counts GEMM operations only (2*M*N*K) over the device time of whole steps with inputs
 resident in HBM; `e2e` is the same metric through the torch operators with pinned host buffers,
 host<->device copies inside the timed region.  `roofline` describes the dominant kernel (the
-tcgen05 CTA-pair GEMM), `cpu_baseline` the CPU restatement of the path timed on this host's cores.
+tcgen05 CTA-pair GEMM; its four launches are timed with CUDA events around CUDA-graph replays, so
+the host's launch cost is not in the figure), `cpu_baseline` the CPU restatement of the path timed
+on this host's cores; `extras` holds the other configurations at one GPU (dynamic quant, W8A8
+decode, W4A16 decode) as GB/s of algorithmic bytes against the measured copy bandwidth.
 With `--impl reference` the CPU path itself is the thing measured.
 """
 from __future__ import annotations
