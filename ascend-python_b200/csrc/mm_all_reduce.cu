@@ -388,12 +388,17 @@ extern "C" int qmm_mm_all_reduce(const int8_t *x1, int64_t ld_x1, const int8_t *
     cudaStream_t s = static_cast<cudaStream_t>(stream);
 
     // Peer-memory path: matmul into this rank's region, then one reduce + gather kernel.
-    if (c.nranks > 1 && c.nranks <= kPeerMaxRanks && comm_turn == 0 && !peer_path_disabled() && N % 8 == 0 &&
+    // (not under stream capture: the epoch advances on the host, a replayed graph would reuse a stale one)
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    QMM_CUDA_OK(cudaStreamIsCapturing(s, &capture));
+    if (capture == cudaStreamCaptureStatusNone && c.nranks > 1 && c.nranks <= kPeerMaxRanks && comm_turn == 0 &&
+        !peer_path_disabled() && N % 8 == 0 &&
         (reinterpret_cast<uintptr_t>(out) & 15) == 0 && c.peer.bytes >= peer_region_bytes(M, N, c.nranks)) {
-        // Row chunks: chunk c's reduce + gather kernel runs on the communication stream while chunk
-        // c+1 is multiplied on the caller's stream.  The two share the SMs: the collective's CTAs need
-        // registers and threads only, the matmul's CTAs all of the shared memory, so one of each fits an
-        // SM, and the NVLink transfers proceed under the tensor work.
+        // Row chunks (QMM_PEER_CHUNKS, default 1): chunk c's reduce + gather kernel can run on the
+        // communication stream while chunk c+1 is multiplied on the caller's stream.  Measured on two
+        // B200s that costs far more than it hides (804-1105 us against 377 us unchunked: the two kernels
+        // share the SMs badly), so the overlap is left to the matmul's epilogue, which pushes finished
+        // tiles to their owners; chunking stays available for experiments.
         int chunks = peer_chunks();
         if (M < 512 * chunks) chunks = 1;
         int64_t rows_chunk = (M + chunks - 1) / chunks;
