@@ -29,6 +29,9 @@ EXPORTED_SYMBOLS = (
     "qmm_comm_unique_id", "qmm_comm_init_rank", "qmm_comm_register", "qmm_comm_info", "qmm_comm_destroy",
     "qmm_mm_all_reduce", "qmm_quant_matmul_decode_noalloc", "qmm_comm_peer_memory_size",
     "qmm_comm_attach_peer_memory",
+    "qmm_w4a16_prepack_size", "qmm_w4a16_prepack", "qmm_w4a16_unpack_weight",
+    "qmm_weight_quant_batchmatmul_prepacked_workspace_size", "qmm_weight_quant_batchmatmul_prepacked",
+    "qmm_rms_norm", "qmm_rms_norm_dynamic_quant", "qmm_comm_stats", "qmm_int8_mma_peak", "qmm_noalloc_status",
 )
 NOALLOC_SCRATCH_BYTES = 16 << 20
 
@@ -90,11 +93,36 @@ def lib() -> ctypes.CDLL:
                                                    c.c_void_p, c.c_int64, c.c_void_p, c.c_void_p, c.c_int64,
                                                    c.c_int64, c.c_int64, c.c_int64, c.c_void_p, c.c_size_t,
                                                    c.c_void_p]
+        L.qmm_w4a16_prepack_size.argtypes = [c.c_int64, c.c_int64, c.c_int64, c.POINTER(c.c_size_t)]
+        L.qmm_w4a16_prepack.argtypes = [c.c_void_p, c.c_int64, c.c_void_p, c.c_void_p, c.c_int, c.c_int64, c.c_int64,
+                                        c.c_int64, c.c_void_p, c.c_size_t, c.c_void_p]
+        L.qmm_w4a16_unpack_weight.argtypes = [c.c_void_p, c.c_int64, c.c_int64, c.c_void_p, c.c_int64, c.c_void_p]
+        L.qmm_weight_quant_batchmatmul_prepacked_workspace_size.argtypes = [c.c_int64, c.c_int64, c.c_int64,
+                                                                            c.POINTER(c.c_size_t)]
+        L.qmm_weight_quant_batchmatmul_prepacked.argtypes = [c.c_void_p, c.c_int, c.c_int64, c.c_void_p, c.c_size_t,
+                                                             c.c_void_p, c.c_void_p, c.c_int64, c.c_int64, c.c_int64,
+                                                             c.c_int64, c.c_void_p, c.c_size_t, c.c_void_p]
+        for name in ("qmm_w4a16_prepack_size", "qmm_w4a16_prepack", "qmm_w4a16_unpack_weight",
+                     "qmm_weight_quant_batchmatmul_prepacked_workspace_size",
+                     "qmm_weight_quant_batchmatmul_prepacked"):
+            getattr(L, name).restype = c.c_int
+        L.qmm_rms_norm.argtypes = [c.c_void_p, c.c_int, c.c_int64, c.c_int64, c.c_int64, c.c_void_p, c.c_double,
+                                   c.c_void_p, c.c_int64, c.c_void_p, c.c_void_p]
+        L.qmm_rms_norm.restype = c.c_int
+        L.qmm_rms_norm_dynamic_quant.argtypes = [c.c_void_p, c.c_int, c.c_int64, c.c_int64, c.c_int64, c.c_void_p,
+                                                 c.c_double, c.c_void_p, c.c_int64, c.c_void_p, c.c_void_p, c.c_void_p]
+        L.qmm_rms_norm_dynamic_quant.restype = c.c_int
+        L.qmm_int8_mma_peak.argtypes = [c.c_int, c.POINTER(c.c_double), c.POINTER(c.c_double), c.POINTER(c.c_double)]
+        L.qmm_int8_mma_peak.restype = c.c_int
+        L.qmm_noalloc_status.argtypes = [c.c_int]
+        L.qmm_noalloc_status.restype = c.c_int
         L.qmm_comm_unique_id.argtypes = [c.c_void_p]
         L.qmm_comm_init_rank.argtypes = [c.c_char_p, c.c_void_p, c.c_int, c.c_int]
         L.qmm_comm_register.argtypes = [c.c_char_p, c.c_void_p, c.c_int, c.c_int]
         L.qmm_comm_info.argtypes = [c.c_char_p, c.POINTER(c.c_int), c.POINTER(c.c_int)]
         L.qmm_comm_destroy.argtypes = [c.c_char_p]
+        L.qmm_comm_stats.argtypes = [c.c_char_p, c.POINTER(c.c_int64), c.POINTER(c.c_int64), c.POINTER(c.c_int64)]
+        L.qmm_comm_stats.restype = c.c_int
         L.qmm_comm_peer_memory_size.argtypes = [c.c_int64, c.c_int64, c.c_int, c.POINTER(c.c_size_t)]
         L.qmm_comm_attach_peer_memory.argtypes = [c.c_char_p, c.POINTER(c.c_void_p), c.c_void_p, c.c_size_t]
         L.qmm_mm_all_reduce.argtypes = [c.c_void_p, c.c_int64, c.c_void_p, c.c_int64, c.c_int64, c.c_void_p,
@@ -225,3 +253,104 @@ def weight_quant_batchmatmul(x, weight, antiquant_scale, antiquant_offset=None, 
             _ptr(None if bias is None else bias.contiguous()), _ptr(out), N, M, N, K, _ptr(ws), ws_bytes, _stream()),
             "qmm_weight_quant_batchmatmul")
     return out
+
+
+def w4a16_prepack_size(N: int, K: int, group: int) -> int:
+    """Bytes of the prepacked form of a [K, N/8] int4 weight (0: this shape cannot be prepacked)."""
+    n = ctypes.c_size_t(0)
+    check(lib().qmm_w4a16_prepack_size(N, K, group, ctypes.byref(n)), "qmm_w4a16_prepack_size")
+    return int(n.value)
+
+
+def w4a16_prepack(weight, antiquant_scale, antiquant_offset=None, group_size=0):
+    """weight int32 [K, N/8] + scale/offset [K/group, N] -> uint8 buffer in the k-major stream layout."""
+    assert weight.is_cuda and weight.dtype == torch.int32
+    K, N = weight.shape[0], weight.shape[1] * 8
+    group = group_size if group_size > 0 else K
+    nbytes = w4a16_prepack_size(N, K, group)
+    if nbytes == 0:
+        raise QmmError(f"W4A16 weights [K={K}, N={N}] with group {group} cannot be prepacked")
+    weight = weight.contiguous()
+    packed = torch.empty(nbytes, dtype=torch.uint8, device=weight.device)
+    with torch.cuda.device(weight.device):
+        check(lib().qmm_w4a16_prepack(_ptr(weight), weight.shape[1], _ptr(antiquant_scale.contiguous()),
+                                      _ptr(None if antiquant_offset is None else antiquant_offset.contiguous()),
+                                      dtype_code(antiquant_scale.dtype), group, N, K, _ptr(packed), nbytes, _stream()),
+              "qmm_w4a16_prepack")
+    return packed
+
+
+def w4a16_unpack_weight(packed, N: int, K: int):
+    """The stock int32 [K, N/8] words back out of a prepacked buffer."""
+    w = torch.empty((K, N // 8), dtype=torch.int32, device=packed.device)
+    with torch.cuda.device(packed.device):
+        check(lib().qmm_w4a16_unpack_weight(_ptr(packed), N, K, _ptr(w), N // 8, _stream()), "qmm_w4a16_unpack_weight")
+    return w
+
+
+def weight_quant_batchmatmul_prepacked(x, packed, N: int, bias=None):
+    """x [M,K] bf16/f16 (the dtype the weights were prepacked with); packed from w4a16_prepack."""
+    assert x.is_cuda and packed.dtype == torch.uint8
+    M, K = x.shape
+    x = x.contiguous()
+    out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    n = ctypes.c_size_t(0)
+    check(lib().qmm_weight_quant_batchmatmul_prepacked_workspace_size(M, N, K, ctypes.byref(n)),
+          "qmm_weight_quant_batchmatmul_prepacked_workspace_size")
+    ws_bytes = int(n.value)
+    ws = get_workspace(x.device, ws_bytes, kind="w4a16_prepacked")
+    with torch.cuda.device(x.device):
+        check(lib().qmm_weight_quant_batchmatmul_prepacked(
+            _ptr(x), dtype_code(x.dtype), K, _ptr(packed), packed.numel(), _ptr(None if bias is None else bias.contiguous()),
+            _ptr(out), N, M, N, K, _ptr(ws), ws_bytes, _stream()), "qmm_weight_quant_batchmatmul_prepacked")
+    return out
+
+
+def _rows_cols(x):
+    cols = x.shape[-1]
+    rows = 1
+    for d in x.shape[:-1]:
+        rows *= d
+    return rows, cols
+
+
+def rms_norm(x: torch.Tensor, gamma: torch.Tensor, epsilon: float = 1e-6):
+    """x [..., cols] bf16/f16/f32, gamma [cols] -> (y like x, rstd fp32 of shape x.shape[:-1] + (1,))."""
+    assert x.is_cuda and gamma.dtype == x.dtype
+    rows, cols = _rows_cols(x)
+    x2 = x.reshape(rows, cols).contiguous()
+    y = torch.empty_like(x2)
+    rstd = torch.empty((rows,), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib().qmm_rms_norm(_ptr(x2), dtype_code(x.dtype), rows, cols, cols, _ptr(gamma.contiguous()), epsilon,
+                                 _ptr(y), cols, _ptr(rstd), _stream()), "qmm_rms_norm")
+    return y.reshape(x.shape), rstd.reshape(*x.shape[:-1], 1)
+
+
+def rms_norm_dynamic_quant(x: torch.Tensor, gamma: torch.Tensor, epsilon: float = 1e-6):
+    """Fused rms_norm + dynamic_quant: (q int8 like x, scale fp32 x.shape[:-1], rstd fp32 x.shape[:-1] + (1,))."""
+    assert x.is_cuda and gamma.dtype == x.dtype
+    rows, cols = _rows_cols(x)
+    x2 = x.reshape(rows, cols).contiguous()
+    q = torch.empty((rows, cols), dtype=torch.int8, device=x.device)
+    scale = torch.empty((rows,), dtype=torch.float32, device=x.device)
+    rstd = torch.empty((rows,), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib().qmm_rms_norm_dynamic_quant(_ptr(x2), dtype_code(x.dtype), rows, cols, cols,
+                                               _ptr(gamma.contiguous()), epsilon, _ptr(q), cols, _ptr(scale),
+                                               _ptr(rstd), _stream()), "qmm_rms_norm_dynamic_quant")
+    return q.reshape(x.shape), scale.reshape(x.shape[:-1]), rstd.reshape(*x.shape[:-1], 1)
+
+
+def comm_stats(name: str) -> dict:
+    """How many qmm_mm_all_reduce calls of communicator `name` took which allreduce path."""
+    a, b, c = ctypes.c_int64(0), ctypes.c_int64(0), ctypes.c_int64(0)
+    check(lib().qmm_comm_stats(name.encode(), ctypes.byref(a), ctypes.byref(b), ctypes.byref(c)), "qmm_comm_stats")
+    return {"peer_calls": a.value, "peer_pushed_calls": b.value, "nccl_calls": c.value}
+
+
+def int8_mma_peak(batches: int = 1024) -> dict:
+    """Measured issue-rate ceiling of the int8 tensor pipe (see qmm_int8_mma_peak)."""
+    a, b, c = ctypes.c_double(0), ctypes.c_double(0), ctypes.c_double(0)
+    check(lib().qmm_int8_mma_peak(batches, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c)), "qmm_int8_mma_peak")
+    return {"ops_per_clk_per_sm": a.value, "tops": b.value, "sm_mhz": c.value}

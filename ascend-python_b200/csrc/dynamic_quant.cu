@@ -17,94 +17,18 @@
 // half-integer.  The tests compare against IEEE division for every pair of bf16 significands and of
 // f16 significands (quotient significands do not depend on exponents), which covers the inputs this
 // operator accepts.  Rows whose scale is tiny, not finite, or has an all-ones significand take
-// true divisions.
+// true divisions.  A row that holds an infinity has an infinite scale (finite elements quantize to 0);
+// a row that holds a NaN has a NaN scale; a quotient that is NaN (Inf / Inf, anything / NaN)
+// quantizes to 0.
 // bf16/f16 inputs make EXACT ties (x / scale = n + 1/2) common - x and amax are short-significand
 // numbers - so a scheme that falls back to a division near ties would fall back all the time.
-#include "qmm_common.cuh"
+#include "dynamic_quant.cuh"
 
 namespace qmm {
 
 namespace {
 
-template <typename T>
-__device__ __forceinline__ void unpack8(const uint4 &v, float (&f)[8]);
-
-template <>
-__device__ __forceinline__ void unpack8<__nv_bfloat16>(const uint4 &v, float (&f)[8]) {
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        f[2 * i] = __uint_as_float(w[i] << 16);
-        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
-}
-
-template <>
-__device__ __forceinline__ void unpack8<__half>(const uint4 &v, float (&f)[8]) {
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        __half2 h = *reinterpret_cast<const __half2 *>(&w[i]);
-        float2 p = __half22float2(h);
-        f[2 * i] = p.x;
-        f[2 * i + 1] = p.y;
-    }
-}
-
-struct RowQuant {
-    float scale;
-    float inv;
-    bool exact_only;  // reciprocal unusable (zero, denormal or non-finite scale)
-};
-
-__device__ __forceinline__ RowQuant make_row_quant(float amax) {
-    RowQuant r;
-    r.scale = __fdiv_rn(amax, 127.0f);
-    r.inv = __frcp_rn(r.scale);
-    // preconditions of the FMA division: no underflow in the remainder, a finite reciprocal, and a
-    // divisor whose significand is not all ones
-    r.exact_only = !(r.scale >= 1e-25f) || !(r.inv <= 3.0e38f) ||
-                   (__float_as_uint(r.scale) & 0x007fffffu) == 0x007fffffu;
-    return r;
-}
-
-__device__ __forceinline__ int quant_one(float x, const RowQuant &rq) {
-    if (rq.scale == 0.0f) return 0;
-    float t;
-    if (rq.exact_only) {
-        t = __fdiv_rn(x, rq.scale);
-    } else {
-        const float q0 = x * rq.inv;
-        t = fmaf(fmaf(-q0, rq.scale, x), rq.inv, q0);
-    }
-    return max(-128, min(127, __float2int_rn(t)));
-}
-
-// absmax of the eight 16-bit floats of a 128-bit vector, packed two at a time
-template <typename T>
-__device__ __forceinline__ float absmax8(const uint4 &v);
-template <>
-__device__ __forceinline__ float absmax8<__nv_bfloat16>(const uint4 &v) {
-    const uint32_t w[4] = {v.x & 0x7fff7fffu, v.y & 0x7fff7fffu, v.z & 0x7fff7fffu, v.w & 0x7fff7fffu};
-    __nv_bfloat162 m = __hmax2(__hmax2(*reinterpret_cast<const __nv_bfloat162 *>(&w[0]),
-                                       *reinterpret_cast<const __nv_bfloat162 *>(&w[1])),
-                               __hmax2(*reinterpret_cast<const __nv_bfloat162 *>(&w[2]),
-                                       *reinterpret_cast<const __nv_bfloat162 *>(&w[3])));
-    return fmaxf(__low2float(m), __high2float(m));
-}
-template <>
-__device__ __forceinline__ float absmax8<__half>(const uint4 &v) {
-    const uint32_t w[4] = {v.x & 0x7fff7fffu, v.y & 0x7fff7fffu, v.z & 0x7fff7fffu, v.w & 0x7fff7fffu};
-    __half2 m = __hmax2(__hmax2(*reinterpret_cast<const __half2 *>(&w[0]), *reinterpret_cast<const __half2 *>(&w[1])),
-                        __hmax2(*reinterpret_cast<const __half2 *>(&w[2]), *reinterpret_cast<const __half2 *>(&w[3])));
-    return fmaxf(__low2float(m), __high2float(m));
-}
-
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
-}
+using namespace dq;
 
 // Vector kernel: `tpr` threads per row, each holding VPT 16-byte vectors.
 template <typename T, int VPT>
@@ -129,7 +53,7 @@ dynamic_quant_vec_kernel(const T *__restrict__ x, int64_t rows, int cols, int64_
             v[i] = idx < nvec ? __ldg(src + idx) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
-        for (int i = 0; i < VPT; ++i) amax = fmaxf(amax, absmax8<T>(v[i]));
+        for (int i = 0; i < VPT; ++i) amax = max_nan(amax, absmax8<T>(v[i]));
     }
     amax = warp_max(amax);
     if (tpr > 32) {
@@ -139,7 +63,7 @@ dynamic_quant_vec_kernel(const T *__restrict__ x, int64_t rows, int cols, int64_
         __syncthreads();
         const int w0 = row_in_cta * warps_per_row;
         float m = 0.0f;
-        for (int w = 0; w < warps_per_row; ++w) m = fmaxf(m, s_part[w0 + w]);
+        for (int w = 0; w < warps_per_row; ++w) m = max_nan(m, s_part[w0 + w]);
         amax = m;
     }
     if (!row_ok) return;
@@ -154,29 +78,7 @@ dynamic_quant_vec_kernel(const T *__restrict__ x, int64_t rows, int cols, int64_
         if (idx < nvec) {
             float f[8];
             unpack8<T>(v[i], f);
-            uint32_t lo = 0, hi = 0;
-            if (fast) {
-                // main path, FMA pipe only: product, exact remainder, corrected quotient, magic-number rounding
-                constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23: adding it rounds to an integer, ties to even
-                uint32_t b[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const float q0 = f[j] * rq.inv;
-                    const float rem = fmaf(-q0, rq.scale, f[j]);
-                    const float q1 = fmaf(rem, rq.inv, q0);  // the IEEE quotient f / scale (see the file header)
-                    b[j] = __float_as_uint(q1 + kMagic);
-                }
-                // the int8 results are the low bytes of the biased floats: gather (b0..b3) and (b4..b7)
-                lo = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
-                hi = __byte_perm(__byte_perm(b[4], b[5], 0x0040), __byte_perm(b[6], b[7], 0x0040), 0x5410);
-            } else {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    lo |= (static_cast<uint32_t>(quant_one(f[j], rq)) & 0xffu) << (8 * j);
-                    hi |= (static_cast<uint32_t>(quant_one(f[4 + j], rq)) & 0xffu) << (8 * j);
-                }
-            }
-            dst[idx] = make_uint2(lo, hi);
+            dst[idx] = quantize8(f, rq, fast);
         }
     }
 }
@@ -192,12 +94,12 @@ dynamic_quant_generic_kernel(const T *__restrict__ x, int64_t rows, int64_t cols
     if (row >= rows) return;
     const T *src = x + row * ld_x;
     float amax = 0.0f;
-    for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) amax = fmaxf(amax, fabsf(to_float(src[c])));
+    for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) amax = max_nan(amax, fabsf(to_float(src[c])));
     amax = warp_max(amax);
     if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = amax;
     __syncthreads();
     float m = 0.0f;
-    for (int w = 0; w < static_cast<int>(blockDim.x >> 5); ++w) m = fmaxf(m, s_part[w]);
+    for (int w = 0; w < static_cast<int>(blockDim.x >> 5); ++w) m = max_nan(m, s_part[w]);
     const RowQuant rq = make_row_quant(m);
     if (threadIdx.x == 0) scale[row] = rq.scale;
     int8_t *dst = q + row * ld_q;

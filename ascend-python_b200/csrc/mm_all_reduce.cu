@@ -17,6 +17,7 @@
 // When the ranks have attached peer memory to the communicator (qmm_comm_attach_peer_memory) and the
 // call fits it, NCCL is not involved: the matmul writes its partial output into this rank's region
 // and one kernel per rank (peer_all_reduce.cuh) reduces and gathers over NVLink loads.
+#include <cstdio>
 #include <dlfcn.h>
 #include <nccl.h>
 
@@ -32,13 +33,10 @@ namespace qmm {
 
 int quant_matmul_dispatch(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
                           const EpilogueParams &ep, int out_dtype, int64_t K, int algo, void *workspace,
-                          size_t workspace_bytes, cudaStream_t stream);
+                          size_t workspace_bytes, cudaStream_t stream, LaunchOptions *opts);
 int validate_quant_matmul(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
                           const float *scale, int64_t scale_len, const void *bias, int bias_dtype, void *out,
                           int out_dtype, int64_t ld_out, int64_t M, int64_t N, int64_t K);
-void set_sm_reserve(int sms);
-void set_push_targets(const PushSpec *spec);
-bool push_applied();
 
 namespace {
 
@@ -134,6 +132,9 @@ struct Comm {
     int rank = 0;
     int device = 0;
     bool owned = false;
+    int64_t stat_peer = 0;         // calls whose allreduce ran in the library's own kernel over peer memory
+    int64_t stat_peer_pushed = 0;  // ... of which the matmul delivered its tiles to the owners itself
+    int64_t stat_nccl = 0;         // calls whose allreduce NCCL carried
     cudaStream_t stream = nullptr;  // communication stream
     cudaEvent_t chunk_ready[kMaxChunks] = {};
     cudaEvent_t done = nullptr;
@@ -251,13 +252,21 @@ namespace {
 
 size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
-// Bytes of a region that an allreduce of [M][N] 16-bit values over `world` ranks needs.
-size_t peer_region_bytes(int64_t M, int64_t N, int world) {
-    // flags; partials, either [M][N] or [world][rows_per][N] with rows_per rounded up to 32; reduced [M][N]
+// A region is its flags followed by two halves of equal size whose position depends on the region's
+// size only: partial outputs ([M][N], or [world][rows_per][N] with rows_per rounded up to 32) in the
+// first, the reduced output [M][N] in the second.  Because the halves never move, a call of one shape
+// may follow a call of another without a barrier between them (see peer_all_reduce.cuh).
+size_t peer_half_need(int64_t M, int64_t N, int world) {
     const int64_t rows_per = ((M + world - 1) / world + 31) / 32 * 32;
-    return kPeerFlagBytes + align256(static_cast<size_t>(world) * rows_per * N * 2) +
-           align256(static_cast<size_t>(M) * N * 2);
+    const size_t a = align256(static_cast<size_t>(world) * rows_per * N * 2);
+    const size_t b = align256(static_cast<size_t>(M) * N * 2);
+    return a > b ? a : b;
 }
+size_t peer_half_bytes(size_t region_bytes) {
+    return region_bytes <= kPeerFlagBytes ? 0 : ((region_bytes - kPeerFlagBytes) / 2) & ~static_cast<size_t>(255);
+}
+// Bytes of a region that an allreduce of [M][N] 16-bit values over `world` ranks needs.
+size_t peer_region_bytes(int64_t M, int64_t N, int world) { return kPeerFlagBytes + 2 * peer_half_need(M, N, world); }
 
 // Row chunks of the peer-memory path (QMM_PEER_CHUNKS, 1..8).
 int peer_chunks() {
@@ -340,6 +349,19 @@ extern "C" int qmm_comm_info(const char *name, int *nranks, int *rank) {
     return QMM_OK;
 }
 
+extern "C" int qmm_comm_stats(const char *name, int64_t *peer_calls, int64_t *peer_pushed_calls, int64_t *nccl_calls) {
+    using namespace qmm;
+    QMM_REQUIRE(name != nullptr, "qmm_comm_stats: name is NULL");
+    std::lock_guard<std::mutex> lock(g_comm_mutex);
+    auto it = g_comms.find(name);
+    if (it == g_comms.end())
+        return fail(QMM_ERR_NOT_FOUND, std::string("communicator '") + name + "' is not registered");
+    if (peer_calls) *peer_calls = it->second.stat_peer;
+    if (peer_pushed_calls) *peer_pushed_calls = it->second.stat_peer_pushed;
+    if (nccl_calls) *nccl_calls = it->second.stat_nccl;
+    return QMM_OK;
+}
+
 extern "C" int qmm_comm_destroy(const char *name) {
     using namespace qmm;
     QMM_REQUIRE(name != nullptr, "qmm_comm_destroy: name is NULL");
@@ -372,6 +394,14 @@ extern "C" int qmm_mm_all_reduce(const int8_t *x1, int64_t ld_x1, const int8_t *
     int rc = validate_quant_matmul(x1, ld_x1, x2, x2_stride_k, x2_stride_n, scale, scale_len, bias, bias_dtype, out,
                                    out_dtype, ld_out, M, N, K);
     if (rc != QMM_OK) return rc;
+    // A bounded wait that gave up in an earlier kernel (a peer that never arrived) left that call's result
+    // incomplete: report it here, where the next collective would otherwise build on it.  The word is cleared.
+    if (const uint32_t st = device_status_peek(true)) {
+        char msg[160];
+        snprintf(msg, sizeof(msg), "qmm_mm_all_reduce: an earlier kernel's bounded device-side wait gave up (status 0x%x); "
+                 "that call's result is incomplete (status cleared)", st);
+        return fail(QMM_ERR_DEVICE_TIMEOUT, msg);
+    }
     Comm c;
     {
         std::lock_guard<std::mutex> lock(g_comm_mutex);
@@ -387,13 +417,20 @@ extern "C" int qmm_mm_all_reduce(const int8_t *x1, int64_t ld_x1, const int8_t *
     QMM_REQUIRE(dev == c.device, "qmm_mm_all_reduce: communicator belongs to another device");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
 
-    // Peer-memory path: matmul into this rank's region, then one reduce + gather kernel.
-    // (not under stream capture: the epoch advances on the host, a replayed graph would reuse a stale one)
-    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
-    QMM_CUDA_OK(cudaStreamIsCapturing(s, &capture));
-    if (capture == cudaStreamCaptureStatusNone && c.nranks > 1 && c.nranks <= kPeerMaxRanks && comm_turn == 0 &&
-        !peer_path_disabled() && N % 8 == 0 &&
-        (reinterpret_cast<uintptr_t>(out) & 15) == 0 && c.peer.bytes >= peer_region_bytes(M, N, c.nranks)) {
+    // Peer-memory path: matmul into this rank's region, then one reduce + gather kernel.  Whether a call
+    // takes it depends only on values every rank shares (shape, attached size, comm_turn, the QMM_ALLREDUCE
+    // setting), so that ranks cannot part ways; what only this rank can see (capture state, alignment of
+    // `out`) is an error instead of a silent switch to NCCL that the peers would not follow.
+    if (c.nranks > 1 && c.nranks <= kPeerMaxRanks && comm_turn == 0 && !peer_path_disabled() && N % 8 == 0 &&
+        peer_half_bytes(c.peer.bytes) >= peer_half_need(M, N, c.nranks)) {
+        cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+        QMM_CUDA_OK(cudaStreamIsCapturing(s, &capture));
+        if (capture != cudaStreamCaptureStatusNone)
+            return fail(QMM_ERR_UNSUPPORTED,
+                        "qmm_mm_all_reduce: the peer-memory allreduce cannot be captured in a CUDA graph (its epoch "
+                        "advances on the host); pass comm_turn > 0 or set QMM_ALLREDUCE=nccl on every rank");
+        QMM_REQUIRE((reinterpret_cast<uintptr_t>(out) & 15) == 0,
+                    "qmm_mm_all_reduce: out must be 16-byte aligned for the peer-memory allreduce");
         // Row chunks (QMM_PEER_CHUNKS, default 1): chunk c's reduce + gather kernel can run on the
         // communication stream while chunk c+1 is multiplied on the caller's stream.  Measured on two
         // B200s that costs far more than it hides (804-1105 us against 377 us unchunked: the two kernels
@@ -405,26 +442,18 @@ extern "C" int qmm_mm_all_reduce(const int8_t *x1, int64_t ld_x1, const int8_t *
         rows_chunk = (rows_chunk + 255) / 256 * 256;
         const size_t elt = 2;
         const int64_t rows_per_full = ((M + c.nranks - 1) / c.nranks + 31) / 32 * 32;
-        const size_t red_area = kPeerFlagBytes + align256(static_cast<size_t>(c.nranks) * rows_per_full * N * elt);
+        const size_t red_area = kPeerFlagBytes + peer_half_bytes(c.peer.bytes);
         const bool push_ok = chunks == 1 && !push_disabled();
         int ci = 0;
         for (int64_t m0 = 0; m0 < M; m0 += rows_chunk, ++ci) {
             const int64_t rows = (M - m0) < rows_chunk ? (M - m0) : rows_chunk;
             const size_t row_bytes0 = static_cast<size_t>(m0) * N * elt;
-            uint32_t epoch = 0;
-            {
-                std::lock_guard<std::mutex> lock(g_comm_mutex);
-                auto it = g_comms.find(hcom);
-                if (it == g_comms.end())
-                    return fail(QMM_ERR_NOT_FOUND, std::string("communicator '") + hcom + "' is not registered");
-                epoch = ++it->second.peer.epoch;
-            }
             PeerParams pp;
             for (int r = 0; r < kPeerMaxRanks; ++r) pp.base[r] = c.peer.base[r];
             pp.mc_base = c.peer.mc_base;
             pp.world = c.nranks;
             pp.rank = c.rank;
-            pp.epoch = epoch;
+            pp.epoch = 0;  // drawn below, once the matmul is in the stream
             pp.M = rows;
             pp.N = N;
             pp.rows_per = chunks == 1 ? rows_per_full : (rows + c.nranks - 1) / c.nranks;
@@ -438,6 +467,7 @@ extern "C" int qmm_mm_all_reduce(const int8_t *x1, int64_t ld_x1, const int8_t *
             pp.red_off = red_area + row_bytes0;
             pp.out = static_cast<uint8_t *>(out) + row_bytes0;
             pp.status = device_status_word();
+            pp.status_at_launch = device_status_peek(false);
             EpilogueParams ep;
             ep.scale = scale;
             ep.pertoken_scale = pertoken_scale ? pertoken_scale + m0 : nullptr;
@@ -450,19 +480,32 @@ extern "C" int qmm_mm_all_reduce(const int8_t *x1, int64_t ld_x1, const int8_t *
             ep.N = N;
             // the CTA-pair matmul stores each output tile into the region of the rank that owns its rows
             PushSpec spec;
+            LaunchOptions opts;
             if (push_ok) {
                 for (int r = 0; r < kPeerMaxRanks; ++r) spec.base[r] = c.peer.base[r];
                 spec.area_off = pp.partial_off;
                 spec.world = c.nranks;
                 spec.rank = c.rank;
                 spec.rows_per = pp.rows_per;
-                set_push_targets(&spec);
+                opts.push = &spec;
             }
             rc = quant_matmul_dispatch(x1 + m0 * ld_x1, ld_x1, x2, x2_stride_k, x2_stride_n, ep, out_dtype, K,
-                                       K == 0 ? QMM_ALGO_SIMT : QMM_ALGO_AUTO, workspace, workspace_bytes, s);
-            pp.pushed = push_applied() ? 1 : 0;
-            set_push_targets(nullptr);
+                                       K == 0 ? QMM_ALGO_SIMT : QMM_ALGO_AUTO, workspace, workspace_bytes, s, &opts);
+            pp.pushed = opts.push_applied ? 1 : 0;
             if (rc != QMM_OK) return rc;
+            // The epoch advances only now: a call that failed before this point has touched no flag, so the
+            // ranks' epochs stay in step as long as every rank either launches or fails before launching.
+            {
+                std::lock_guard<std::mutex> lock(g_comm_mutex);
+                auto it = g_comms.find(hcom);
+                if (it == g_comms.end())
+                    return fail(QMM_ERR_NOT_FOUND, std::string("communicator '") + hcom + "' is not registered");
+                pp.epoch = ++it->second.peer.epoch;
+                if (ci == 0) {
+                    ++it->second.stat_peer;
+                    if (pp.pushed) ++it->second.stat_peer_pushed;
+                }
+            }
             cudaStream_t ks = s;
             if (chunks > 1) {
                 QMM_CUDA_OK(cudaEventRecord(c.chunk_ready[ci], s));
@@ -518,10 +561,10 @@ extern "C" int qmm_mm_all_reduce(const int8_t *x1, int64_t ld_x1, const int8_t *
         ep.M = rows;
         ep.N = N;
         // leave SMs to a collective that may be running beside this chunk
-        set_sm_reserve((c.nranks > 1 && ci > 0) ? comm_ctas() : 0);
+        LaunchOptions opts;
+        opts.sm_reserve = (c.nranks > 1 && ci > 0) ? comm_ctas() : 0;
         rc = quant_matmul_dispatch(x1 + m0 * ld_x1, ld_x1, x2, x2_stride_k, x2_stride_n, ep, out_dtype, K,
-                                   K == 0 ? QMM_ALGO_SIMT : QMM_ALGO_AUTO, workspace, workspace_bytes, s);
-        set_sm_reserve(0);
+                                   K == 0 ? QMM_ALGO_SIMT : QMM_ALGO_AUTO, workspace, workspace_bytes, s, &opts);
         if (rc != QMM_OK) return rc;
         if (c.nranks > 1) {
             QMM_CUDA_OK(cudaEventRecord(c.chunk_ready[ci], s));
@@ -531,6 +574,11 @@ extern "C" int qmm_mm_all_reduce(const int8_t *x1, int64_t ld_x1, const int8_t *
         }
     }
     if (c.nranks > 1) {
+        {
+            std::lock_guard<std::mutex> lock(g_comm_mutex);
+            auto it = g_comms.find(hcom);
+            if (it != g_comms.end()) ++it->second.stat_nccl;
+        }
         QMM_CUDA_OK(cudaEventRecord(c.done, c.stream));
         QMM_CUDA_OK(cudaStreamWaitEvent(s, c.done, 0));
         ncclResult_t async = ncclSuccess;

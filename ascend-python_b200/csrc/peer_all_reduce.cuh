@@ -28,10 +28,11 @@
 // again.  Flags carry the call's epoch, which only grows, so they are never reset.
 //
 // Buffer reuse across calls needs no extra synchronisation: a rank finishes step 3 only after all
-// peers have raised all their B flags, i.e. after they are done reading partials (its own, or - with
-// pushed tiles - the area its next matmul will write into); and it overwrites its reduced rows in
+// peers have raised all their B flags, i.e. after they are done reading the partial halves (its own, or
+// - with pushed tiles - the one its next matmul will write into); and it overwrites the reduced half in
 // the next call only after all peers have raised the next A flag, i.e. after their previous kernel,
-// which read those rows, has ended.
+// which read that half, has ended.  Partial data never lands in a reduced half or the other way round,
+// whatever M and N the next call has.
 #pragma once
 
 #include "qmm_common.cuh"
@@ -60,6 +61,7 @@ struct PeerParams {
     size_t partial_off, red_off;   // byte offsets of the two data areas inside a region
     void *out;                     // [M][N], this rank's result
     uint32_t *status;
+    uint32_t status_at_launch;     // value of *status when the host launched this kernel: only a CHANGE aborts a wait
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
@@ -75,7 +77,10 @@ __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
 // The poll backs off with nanosleep: hundreds of CTAs polling at full speed (system-scope loads, plus
 // reads of the host-mapped status word) were measured to slow the very transfers they wait for by
 // several times.
-__device__ __noinline__ bool peer_wait_flag(const uint32_t *flag, uint32_t epoch, uint32_t *status, uint32_t where) {
+// A wait also gives up when the process-wide status word changes while it polls (some kernel of this process
+// recorded a timeout): compared with the value at launch, so that an old, unread code does not abort later calls.
+__device__ __noinline__ bool peer_wait_flag(const uint32_t *flag, uint32_t epoch, uint32_t *status, uint32_t status0,
+                                            uint32_t where) {
     if (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) >= 0) return true;
     const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
@@ -83,7 +88,7 @@ __device__ __noinline__ bool peer_wait_flag(const uint32_t *flag, uint32_t epoch
         __nanosleep(spins < 16 ? 100 : 400);
         if (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) >= 0) return true;
         if (((++spins) & 0xfffu) == 0) {  // every millisecond or two
-            if (status != nullptr && *reinterpret_cast<volatile uint32_t *>(status) != 0) return false;
+            if (status != nullptr && *reinterpret_cast<volatile uint32_t *>(status) != status0) return false;
             if (globaltimer_ns() - t0 > kWaitLimitNs) {
                 if (status != nullptr) atomicMax(status, DEV_STATUS_PEER_TIMEOUT | where);
                 return false;
@@ -191,7 +196,7 @@ __global__ void __launch_bounds__(kPeerThreads, 1) peer_all_reduce_kernel(PeerPa
     if (threadIdx.x == 0) s_ok = 1;
     __syncthreads();
     if (threadIdx.x < W) {
-        if (!peer_wait_flag(my_flags + threadIdx.x, p.epoch, p.status, 0x01)) s_ok = 0;
+        if (!peer_wait_flag(my_flags + threadIdx.x, p.epoch, p.status, p.status_at_launch, 0x01)) s_ok = 0;
     }
     __syncthreads();
     if (!s_ok) return;
@@ -254,7 +259,8 @@ __global__ void __launch_bounds__(kPeerThreads, 1) peer_all_reduce_kernel(PeerPa
         chunk_bounds(src_vecs, c, p.nchunks, lo, hi);
         __syncthreads();  // s_ok of the previous item has been read by everyone
         if (threadIdx.x == 0)
-            s_ok = peer_wait_flag(my_b + static_cast<size_t>(src) * kPeerChunks + c, p.epoch, p.status, 0x02) ? 1 : 0;
+            s_ok = peer_wait_flag(my_b + static_cast<size_t>(src) * kPeerChunks + c, p.epoch, p.status, p.status_at_launch,
+                                  0x02) ? 1 : 0;
         __syncthreads();
         if (!s_ok) return;
         // reduced rows of `src`: in its region, or (multicast) already in this rank's own region

@@ -36,6 +36,8 @@ int fail(int code, const std::string &msg);
 // Device-visible status word (host-mapped, one per process). Kernels write a
 // non-zero code when a bounded wait gives up; see qmm_device_status().
 uint32_t *device_status_word();
+// Host-side view of that word without creating it (0 if it does not exist yet); `clear` resets it.
+uint32_t device_status_peek(bool clear);
 
 // Number of SMs of the current device (cached per device).
 int sm_count();
@@ -240,6 +242,93 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
           "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
+}
+
+// 32 lanes x 16 consecutive 32-bit columns, registers -> TMEM: thread i of the warp writes lane
+// (base_lane + i), r[0..15] = columns col..col+15.  Complete (for this thread) after tmem_st_wait().
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// D[tmem] (+)= A[tmem] * B[smem desc], bf16/f16 -> fp32, issued by one elected lane of a converged
+// warp.  A lives in tensor memory: row i of the 128-row operand in lane i, two consecutive k per
+// 32-bit column (low half = even k), so a K=16 MMA reads eight columns starting at `a_tmem`.
+__device__ __forceinline__ void mma_f16_ts_warp(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Eight K=16 MMAs of one 128-row block under one election: A = 64 consecutive tensor-memory columns
+// starting at `a_tmem` (eight columns per MMA), B = two K-major 128-byte-swizzled boxes of 64 k each
+// (`b_lo0`, `b_lo1`: low descriptor halves of the boxes; 32 bytes = +2 per MMA within a box).  The first
+// MMA accumulates only if `accumulate` is set, the others always.
+__device__ __forceinline__ void mma_f16_ts_warp_x8(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo0, uint32_t b_lo1,
+                                                   uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, e, t;\n\t"
+        ".reg .b64 bd;\n\t"
+        ".reg .b32 a, bl;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "setp.eq.b32 t, 0, 0;\n\t"
+        "mov.b64 bd, {%2, %4};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], bd, %5, p;\n\t"
+        "add.u32 a, %1, 8;\n\t"
+        "add.u32 bl, %2, 2;\n\t"
+        "mov.b64 bd, {bl, %4};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [a], bd, %5, t;\n\t"
+        "add.u32 a, %1, 16;\n\t"
+        "add.u32 bl, %2, 4;\n\t"
+        "mov.b64 bd, {bl, %4};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [a], bd, %5, t;\n\t"
+        "add.u32 a, %1, 24;\n\t"
+        "add.u32 bl, %2, 6;\n\t"
+        "mov.b64 bd, {bl, %4};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [a], bd, %5, t;\n\t"
+        "add.u32 a, %1, 32;\n\t"
+        "mov.b64 bd, {%3, %4};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [a], bd, %5, t;\n\t"
+        "add.u32 a, %1, 40;\n\t"
+        "add.u32 bl, %3, 2;\n\t"
+        "mov.b64 bd, {bl, %4};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [a], bd, %5, t;\n\t"
+        "add.u32 a, %1, 48;\n\t"
+        "add.u32 bl, %3, 4;\n\t"
+        "mov.b64 bd, {bl, %4};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [a], bd, %5, t;\n\t"
+        "add.u32 a, %1, 56;\n\t"
+        "add.u32 bl, %3, 6;\n\t"
+        "mov.b64 bd, {bl, %4};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [a], bd, %5, t;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "r"(b_lo0), "r"(b_lo1), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Untiled bulk copy global -> shared (this CTA), completion bytes counted on an mbarrier.
+// Both addresses 16-byte aligned, `bytes` a multiple of 16.
+__device__ __forceinline__ void bulk_load_1d(uint32_t smem_dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_dst),
+                 "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+                 : "memory");
 }
 
 // ---- CTA pairs (cluster of 2, tcgen05 cta_group::2) ---------------------------

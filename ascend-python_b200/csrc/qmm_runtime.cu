@@ -46,6 +46,15 @@ uint32_t *device_status_word() {
     return g_status_dev;
 }
 
+// Current value of the status word as the host sees it (0 if it was never created); `clear` resets it.
+uint32_t device_status_peek(bool clear) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (g_status_host == nullptr) return 0;
+    const uint32_t v = *reinterpret_cast<volatile uint32_t *>(g_status_host);
+    if (clear && v != 0) *reinterpret_cast<volatile uint32_t *>(g_status_host) = 0;
+    return v;
+}
+
 int sm_count() {
     static int cached[64] = {0};
     int dev = 0;

@@ -25,12 +25,18 @@ struct EpilogueParams {
 
 // Row-parallel matmul whose output tiles go straight to the rank that will reduce them: rank o owns the
 // rows [o * rows_per, (o+1) * rows_per) and receives them from rank s at
-// base[o] + area_off + s * rows_per * N * element size.  Host-side description (see set_push_targets).
+// base[o] + area_off + s * rows_per * N * element size.  Host-side description (see LaunchOptions).
 struct PushSpec {
     uint8_t *base[8];
     size_t area_off;
     int world, rank;
     int64_t rows_per;  // a multiple of 32, so the 32 rows of an epilogue warp have one owner
+};
+// What a caller of quant_matmul_dispatch may ask of the launch beyond the problem itself.
+struct LaunchOptions {
+    int sm_reserve = 0;              // SMs the persistent kernels leave idle (a collective runs beside them)
+    const PushSpec *push = nullptr;  // owners' receive areas for the output tiles (CTA-pair kernel only)
+    bool push_applied = false;       // out: the launch did deliver its tiles to the owners
 };
 // Kernel-side form: one output tensor map per owner.
 struct PushMaps {

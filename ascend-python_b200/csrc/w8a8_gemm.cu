@@ -21,27 +21,10 @@
 
 namespace qmm {
 
-// SMs the persistent tile kernel leaves idle (set around launches that overlap a collective).
-static thread_local int g_sm_reserve = 0;
-void set_sm_reserve(int sms) { g_sm_reserve = sms < 0 ? 0 : sms; }
-int pair_sm_reserve() { return g_sm_reserve; }
-
-// Push targets for the next quant_matmul_dispatch of this thread (set and cleared by the matmul +
-// allreduce operator).  Only the CTA-pair kernel honours them; push_applied() tells the caller whether
-// the launch that just happened did.
-static thread_local const PushSpec *g_push_spec = nullptr;
-static thread_local bool g_push_applied = false;
-void set_push_targets(const PushSpec *spec) {
-    g_push_spec = spec;
-    g_push_applied = false;
-}
-const PushSpec *pair_push_targets() { return g_push_spec; }
-void mark_push_applied() { g_push_applied = true; }
-bool push_applied() { return g_push_applied; }
-
 // Implemented in w8a8_gemm_pair.cu
 int launch_pair(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
-                const struct EpilogueParams &ep, int out_dtype, int64_t K, cudaStream_t stream);
+                const struct EpilogueParams &ep, int out_dtype, int64_t K, struct LaunchOptions *opts,
+                cudaStream_t stream);
 
 namespace {
 
@@ -343,7 +326,7 @@ w8a8_simt_kernel(const int8_t *__restrict__ x1, int64_t ld_x1, const int8_t *__r
 // ---------------------------------------------------------------------------
 template <typename OutT>
 int launch_tile(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
-                const EpilogueParams &ep, int64_t K, cudaStream_t stream) {
+                const EpilogueParams &ep, int64_t K, int sm_reserve, cudaStream_t stream) {
     CUtensorMap ta, tb;
     int rc = make_tmap_2d(&ta, x1, 1, static_cast<uint64_t>(K), static_cast<uint64_t>(ep.M),
                           static_cast<uint64_t>(ld_x1), kBK, kBM, true);
@@ -369,7 +352,7 @@ int launch_tile(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk
         use_tma_store = 1;
     }
     const int tiles = static_cast<int>(((ep.M + kBM - 1) / kBM) * ((ep.N + kBN - 1) / kBN));
-    int ctas = sm_count() - g_sm_reserve;
+    int ctas = sm_count() - sm_reserve;
     if (ctas < 1) ctas = 1;
     const int grid = tiles < ctas ? tiles : ctas;
     uint32_t *status = device_status_word();
@@ -430,7 +413,7 @@ size_t splitk_scratch_bytes(int64_t M, int64_t N, int64_t K) {
 
 template <typename OutT>
 int launch_tile_splitk(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
-                       const EpilogueParams &ep, int64_t K, void *workspace, cudaStream_t stream) {
+                       const EpilogueParams &ep, int64_t K, void *workspace, int sm_reserve, cudaStream_t stream) {
     const int slices = splitk_slices(ep.M, ep.N, K);
     const int64_t slice_rows = (ep.M + kBM - 1) / kBM * kBM;
     CUtensorMap ta, tb, tout;
@@ -460,7 +443,7 @@ int launch_tile_splitk(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_
     raw.M = ep.M;
     raw.N = ep.N;
     const int items = static_cast<int>(((ep.M + kBM - 1) / kBM) * ((ep.N + kBN - 1) / kBN)) * slices;
-    int ctas = sm_count() - g_sm_reserve;
+    int ctas = sm_count() - sm_reserve;
     if (ctas < 1) ctas = 1;
     const int grid = items < ctas ? items : ctas;
     auto kern = mn_major ? w8a8_tile_kernel<int32_t, true> : w8a8_tile_kernel<int32_t, false>;
@@ -521,7 +504,8 @@ bool streamk_supported(int64_t M, int64_t N, int64_t K, int64_t x2_sn);
 
 int quant_matmul_dispatch(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
                           const EpilogueParams &ep, int out_dtype, int64_t K, int algo, void *workspace,
-                          size_t workspace_bytes, cudaStream_t stream) {
+                          size_t workspace_bytes, cudaStream_t stream, LaunchOptions *opts) {
+    const int sm_reserve = (opts != nullptr && opts->sm_reserve > 0) ? opts->sm_reserve : 0;
     const bool tma_ok = tma_compatible(x1, ld_x1, x2, x2_sk, x2_sn) && K < (1ll << 31) && ep.M < (1ll << 31) &&
                         ep.N < (1ll << 31);
     if (algo == QMM_ALGO_AUTO) {
@@ -547,14 +531,14 @@ int quant_matmul_dispatch(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int
         case QMM_ALGO_TCGEN05_TILE:
             switch (out_dtype) {
                 case QMM_DTYPE_BF16:
-                    return launch_tile<__nv_bfloat16>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, stream);
+                    return launch_tile<__nv_bfloat16>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, sm_reserve, stream);
                 case QMM_DTYPE_F16:
-                    return launch_tile<__half>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, stream);
+                    return launch_tile<__half>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, sm_reserve, stream);
                 default:
-                    return launch_tile<int32_t>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, stream);
+                    return launch_tile<int32_t>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, sm_reserve, stream);
             }
         case QMM_ALGO_TCGEN05_PAIR:
-            return launch_pair(x1, ld_x1, x2, x2_sk, x2_sn, ep, out_dtype, K, stream);
+            return launch_pair(x1, ld_x1, x2, x2_sk, x2_sn, ep, out_dtype, K, opts, stream);
         case QMM_ALGO_TCGEN05_SPLITK:
             if (workspace == nullptr || splitk_scratch_bytes(ep.M, ep.N, K) == 0 ||
                 workspace_bytes < splitk_scratch_bytes(ep.M, ep.N, K) ||
@@ -564,11 +548,11 @@ int quant_matmul_dispatch(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int
                             "4 and the scratch qmm_quant_matmul_workspace_size reports");
             switch (out_dtype) {
                 case QMM_DTYPE_BF16:
-                    return launch_tile_splitk<__nv_bfloat16>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, workspace, stream);
+                    return launch_tile_splitk<__nv_bfloat16>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, workspace, sm_reserve, stream);
                 case QMM_DTYPE_F16:
-                    return launch_tile_splitk<__half>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, workspace, stream);
+                    return launch_tile_splitk<__half>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, workspace, sm_reserve, stream);
                 default:
-                    return launch_tile_splitk<int32_t>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, workspace, stream);
+                    return launch_tile_splitk<int32_t>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, workspace, sm_reserve, stream);
             }
         case QMM_ALGO_TCGEN05_STREAMK:
             return launch_streamk(x1, ld_x1, x2, x2_sk, x2_sn, ep, out_dtype, K, workspace, workspace_bytes, stream);
@@ -653,5 +637,5 @@ extern "C" int qmm_quant_matmul(const int8_t *x1, int64_t ld_x1, const int8_t *x
     ep.N = N;
     if (K == 0) algo = QMM_ALGO_SIMT;  // empty reduction: epilogue of zeros
     return quant_matmul_dispatch(x1, ld_x1, x2, x2_stride_k, x2_stride_n, ep, out_dtype, K, algo, workspace,
-                                 workspace_bytes, static_cast<cudaStream_t>(stream));
+                                 workspace_bytes, static_cast<cudaStream_t>(stream), nullptr);
 }

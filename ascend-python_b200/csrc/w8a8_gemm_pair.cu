@@ -21,9 +21,6 @@
 
 namespace qmm {
 
-int pair_sm_reserve();  // SMs to leave idle (set by callers that overlap a collective)
-const PushSpec *pair_push_targets();  // owners' receive areas for the output tiles, or nullptr
-void mark_push_applied();
 
 namespace {
 
@@ -303,7 +300,7 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
 template <typename OutT>
 int launch_pair_t(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
-                  const EpilogueParams &ep, int64_t K, cudaStream_t stream) {
+                  const EpilogueParams &ep, int64_t K, LaunchOptions *opts, cudaStream_t stream) {
     CUtensorMap ta, tb;
     int rc = make_tmap_2d(&ta, x1, 1, static_cast<uint64_t>(K), static_cast<uint64_t>(ep.M),
                           static_cast<uint64_t>(ld_x1), kPK, kPM, true);
@@ -326,7 +323,7 @@ int launch_pair_t(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_
         use_tma_store = 1;
     }
     const int tiles = static_cast<int>(((ep.M + 2 * kPM - 1) / (2 * kPM)) * ((ep.N + kPN - 1) / kPN));
-    int pairs = (sm_count() - pair_sm_reserve()) / 2;
+    int pairs = (sm_count() - (opts != nullptr && opts->sm_reserve > 0 ? opts->sm_reserve : 0)) / 2;
     if (pairs < 1) pairs = 1;
     if (tiles < pairs) pairs = tiles;
     uint32_t *status = device_status_word();
@@ -348,7 +345,7 @@ int launch_pair_t(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_
     const int raster = pair_choose_raster(ep.M, ep.N, K, static_cast<int64_t>(sizeof(OutT)), pairs);
     PushMaps push;
     memset(&push, 0, sizeof(push));
-    if (const PushSpec *ps = pair_push_targets()) {
+    if (const PushSpec *ps = (opts != nullptr ? opts->push : nullptr)) {
         if (use_tma_store && sizeof(OutT) == 2 && ps->rows_per % 32 == 0 && ep.ld_out == ep.N) {
             for (int o = 0; o < ps->world; ++o) {
                 const int64_t row0 = static_cast<int64_t>(o) * ps->rows_per;
@@ -366,7 +363,7 @@ int launch_pair_t(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_
             }
             push.rows_per = ps->rows_per;
             push.enabled = 1;
-            mark_push_applied();
+            opts->push_applied = true;
         }
     }
     QMM_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ta, tb, tout, push, ep, static_cast<int>(K), use_tma_store, raster,
@@ -377,14 +374,14 @@ int launch_pair_t(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_
 }  // namespace
 
 int launch_pair(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
-                const EpilogueParams &ep, int out_dtype, int64_t K, cudaStream_t stream) {
+                const EpilogueParams &ep, int out_dtype, int64_t K, LaunchOptions *opts, cudaStream_t stream) {
     switch (out_dtype) {
         case QMM_DTYPE_BF16:
-            return launch_pair_t<__nv_bfloat16>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, stream);
+            return launch_pair_t<__nv_bfloat16>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, opts, stream);
         case QMM_DTYPE_F16:
-            return launch_pair_t<__half>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, stream);
+            return launch_pair_t<__half>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, opts, stream);
         default:
-            return launch_pair_t<int32_t>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, stream);
+            return launch_pair_t<int32_t>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, opts, stream);
     }
 }
 

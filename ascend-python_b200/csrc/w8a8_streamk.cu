@@ -347,7 +347,8 @@ size_t streamk_workspace_bytes(int64_t M, int64_t N, int64_t K) {
 
 template <typename OutT>
 static int launch_streamk_t(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
-                            const EpilogueParams &ep, int64_t K, void *workspace, cudaStream_t stream) {
+                            const EpilogueParams &ep, int64_t K, void *workspace, uint32_t *status,
+                            cudaStream_t stream) {
     SkParams p;
     p.ep = ep;
     p.K = static_cast<int>(K);
@@ -360,7 +361,7 @@ static int launch_streamk_t(const int8_t *x1, int64_t ld_x1, const int8_t *x2, i
     const size_t acc_bytes = static_cast<size_t>((ep.N + kSkTileN - 1) / kSkTileN) * p.mpad * kSkTileN * sizeof(int32_t);
     p.ws_acc = static_cast<int32_t *>(workspace);
     p.ws_count = reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(workspace) + acc_bytes);
-    p.status = device_status_word();
+    p.status = status;  // where a bounded wait that gives up records its code
 
     const bool mn_major = (x2_sn == 1);
     CUtensorMap tw, tx;
@@ -399,11 +400,11 @@ int launch_streamk(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2
         return fail(QMM_ERR_WORKSPACE, "qmm_quant_matmul: workspace must be 16-byte aligned");
     switch (out_dtype) {
         case QMM_DTYPE_BF16:
-            return launch_streamk_t<__nv_bfloat16>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, workspace, stream);
+            return launch_streamk_t<__nv_bfloat16>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, workspace, device_status_word(), stream);
         case QMM_DTYPE_F16:
-            return launch_streamk_t<__half>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, workspace, stream);
+            return launch_streamk_t<__half>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, workspace, device_status_word(), stream);
         default:
-            return launch_streamk_t<int32_t>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, workspace, stream);
+            return launch_streamk_t<int32_t>(x1, ld_x1, x2, x2_sk, x2_sn, ep, K, workspace, device_status_word(), stream);
     }
 }
 
@@ -428,15 +429,19 @@ namespace {
 // Scratch of the no-allocation entry point.  Every device that loads the library
 // holds these 16 MiB until the process exits.
 static __device__ __align__(256) uint8_t g_noalloc_scratch[QMM_NOALLOC_SCRATCH_BYTES];
+// Where a kernel launched through this entry point records a bounded wait that gave up (the process-wide
+// status word of the other entry points lives in allocated host memory, which this path must not create).
+static __device__ uint32_t g_noalloc_status;
 
 constexpr int kMaxDevices = 64;
 std::mutex g_noalloc_mutex;
 void *g_noalloc_ptr[kMaxDevices] = {};
+uint32_t *g_noalloc_status_ptr[kMaxDevices] = {};
 
 // Device address of g_noalloc_scratch on the current device.  In host code the
 // array's name is only a handle for the runtime, not an address a kernel could
 // use, so the address is looked up once per device (with that device current).
-int noalloc_scratch_address(void **out) {
+int noalloc_scratch_address(void **out, uint32_t **status_out) {
     int dev = 0;
     QMM_CUDA_OK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= kMaxDevices) return fail(QMM_ERR_UNSUPPORTED, "device ordinal beyond 63");
@@ -446,51 +451,15 @@ int noalloc_scratch_address(void **out) {
         cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
         if (e != cudaSuccess || p == nullptr)
             return fail(QMM_ERR_CUDA, std::string("cudaGetSymbolAddress(g_noalloc_scratch): ") + cudaGetErrorString(e));
+        void *st = nullptr;
+        e = cudaGetSymbolAddress(&st, g_noalloc_status);
+        if (e != cudaSuccess || st == nullptr)
+            return fail(QMM_ERR_CUDA, std::string("cudaGetSymbolAddress(g_noalloc_status): ") + cudaGetErrorString(e));
         g_noalloc_ptr[dev] = p;
+        g_noalloc_status_ptr[dev] = static_cast<uint32_t *>(st);
     }
     *out = g_noalloc_ptr[dev];
-    return QMM_OK;
-}
-
-template <typename OutT>
-int launch_streamk_noalloc_t(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk, int64_t x2_sn,
-                             const EpilogueParams &ep, int64_t K, void *scratch, cudaStream_t stream) {
-    SkParams p;
-    p.ep = ep;
-    p.K = static_cast<int>(K);
-    p.mpad = mpad_of(ep.M);
-    p.stage_bytes = kSkABytes + p.mpad * kSkBK;
-    int stages = static_cast<int>((kSkSmemBudget - 1024 - sizeof(SkSmemTail)) / p.stage_bytes);
-    p.stages = stages > kSkMaxStages ? kSkMaxStages : stages;
-    p.tiles_n = static_cast<int>((ep.N + kSkUnitN - 1) / kSkUnitN);
-    p.kblocks = static_cast<int>((K + kSkBK - 1) / kSkBK);
-    const size_t acc_bytes = static_cast<size_t>((ep.N + kSkTileN - 1) / kSkTileN) * p.mpad * kSkTileN * sizeof(int32_t);
-    p.ws_acc = static_cast<int32_t *>(scratch);
-    p.ws_count = reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(scratch) + acc_bytes);
-    p.status = nullptr;  // the status word lives in allocated host memory; this path reports no timeouts
-
-    const bool mn_major = (x2_sn == 1);
-    CUtensorMap tw, tx;
-    int rc;
-    if (mn_major)
-        rc = make_tmap_2d(&tw, x2, 1, static_cast<uint64_t>(ep.N), static_cast<uint64_t>(K),
-                          static_cast<uint64_t>(x2_sk), 128, kSkBK, true);
-    else
-        rc = make_tmap_2d(&tw, x2, 1, static_cast<uint64_t>(K), static_cast<uint64_t>(ep.N),
-                          static_cast<uint64_t>(x2_sn), kSkBK, kSkUnitN, true);
-    if (rc != QMM_OK) return rc;
-    rc = make_tmap_2d(&tx, x1, 1, static_cast<uint64_t>(K), static_cast<uint64_t>(ep.M),
-                      static_cast<uint64_t>(ld_x1), kSkBK, static_cast<uint32_t>(p.mpad), true);
-    if (rc != QMM_OK) return rc;
-
-    const int64_t total = static_cast<int64_t>(p.tiles_n) * p.kblocks;
-    const int grid = total < sm_count() ? static_cast<int>(total) : sm_count();
-    const size_t smem = 1024 + static_cast<size_t>(p.stages) * p.stage_bytes + sizeof(SkSmemTail);
-    auto kern = mn_major ? w8a8_streamk_kernel<OutT, true> : w8a8_streamk_kernel<OutT, false>;
-    QMM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     static_cast<int>(kSkSmemBudget)));
-    kern<<<grid, kSkThreads, smem, stream>>>(tw, tx, p);
-    QMM_CUDA_OK(cudaGetLastError());
+    *status_out = g_noalloc_status_ptr[dev];
     return QMM_OK;
 }
 
@@ -529,7 +498,8 @@ extern "C" int qmm_quant_matmul_decode_noalloc(const int8_t *x1, int64_t ld_x1, 
         return fail(QMM_ERR_UNSUPPORTED,
                     "qmm_quant_matmul_decode_noalloc: operands need 16-byte aligned addresses and row pitches");
     void *scratch = nullptr;
-    rc = noalloc_scratch_address(&scratch);
+    uint32_t *status = nullptr;
+    rc = noalloc_scratch_address(&scratch, &status);
     if (rc != QMM_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // The array keeps whatever the previous call left (zeros, unless that call was
@@ -547,10 +517,24 @@ extern "C" int qmm_quant_matmul_decode_noalloc(const int8_t *x1, int64_t ld_x1, 
     ep.N = N;
     switch (out_dtype) {
         case QMM_DTYPE_BF16:
-            return launch_streamk_noalloc_t<__nv_bfloat16>(x1, ld_x1, x2, x2_stride_k, x2_stride_n, ep, K, scratch, s);
+            return launch_streamk_t<__nv_bfloat16>(x1, ld_x1, x2, x2_stride_k, x2_stride_n, ep, K, scratch, status, s);
         case QMM_DTYPE_F16:
-            return launch_streamk_noalloc_t<__half>(x1, ld_x1, x2, x2_stride_k, x2_stride_n, ep, K, scratch, s);
+            return launch_streamk_t<__half>(x1, ld_x1, x2, x2_stride_k, x2_stride_n, ep, K, scratch, status, s);
         default:
-            return launch_streamk_noalloc_t<int32_t>(x1, ld_x1, x2, x2_stride_k, x2_stride_n, ep, K, scratch, s);
+            return launch_streamk_t<int32_t>(x1, ld_x1, x2, x2_stride_k, x2_stride_n, ep, K, scratch, status, s);
     }
+}
+
+extern "C" int qmm_noalloc_status(int reset) {
+    using namespace qmm;
+    uint32_t v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_noalloc_status, sizeof(v)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return -1;
+    }
+    if (reset && v != 0) {
+        const uint32_t zero = 0;
+        (void)cudaMemcpyToSymbol(g_noalloc_status, &zero, sizeof(zero));
+    }
+    return static_cast<int>(v);
 }

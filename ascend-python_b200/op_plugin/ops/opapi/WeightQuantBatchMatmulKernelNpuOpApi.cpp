@@ -6,10 +6,122 @@
 // bias handling of op_plugin/ops/base_ops/aclops/LinearKernelNpu.cpp:29-45.
 // Weight layout: int32 tensor [K, N/8]; nibble j of word i is column 8*i+j,
 // two's complement.  W = (w + antiquant_offset) * antiquant_scale.
+//
+// Weight format.  The reference keeps matmul weights in a private device format and casts between it and
+// the plain layout around the matmul (ND <-> FRACTAL_NZ, op_plugin/ops/base_ops/aclops/MmKernelNpu.cpp:80-94,
+// :301-316).  The counterpart here is the k-major int4 stream of qmm_w4a16_prepack: the first call that
+// benefits from it (more than eight token rows) rewrites the weight once, and a cache keyed by the data
+// pointers of weight, scale and offset serves every later call.  An entry stays valid while the three
+// storages are alive and their version counters are unchanged (an in-place update re-packs); the cache holds
+// a second copy of the weights, bounded by QMM_W4_PREPACK_MAX_MB (default 16384; QMM_W4_PREPACK=0 switches
+// the format off).  Callers that want a single copy prepack explicitly through the C ABI and drop the original.
+#include <cstdlib>
+#include <map>
+#include <mutex>
+#include <optional>
+#include <tuple>
+
 #include "op_plugin/OpApiInterface.h"
 #include "op_plugin/utils/qmm_api_common.h"
 
 namespace op_api {
+
+namespace {
+
+struct PrepackEntry {
+    at::Tensor packed;
+    std::optional<c10::weak_intrusive_ptr<c10::StorageImpl>> storages[3];
+    uint32_t versions[3] = {0, 0, 0};
+};
+
+using PrepackKey = std::tuple<const void *, const void *, const void *, int64_t, int64_t, int64_t, int>;
+
+uint32_t version_of(const at::Tensor &t)
+{
+    return t.is_inference() ? 0u : t.unsafeGetTensorImpl()->version_counter().current_version();
+}
+
+bool prepack_enabled()
+{
+    static const bool on = [] {
+        const char *e = std::getenv("QMM_W4_PREPACK");
+        return !(e != nullptr && std::string(e) == "0");
+    }();
+    return on;
+}
+
+size_t prepack_budget_bytes()
+{
+    static const size_t n = [] {
+        const char *e = std::getenv("QMM_W4_PREPACK_MAX_MB");
+        const long long mb = e ? std::atoll(e) : 16384;
+        return static_cast<size_t>(mb < 0 ? 0 : mb) << 20;
+    }();
+    return n;
+}
+
+// The prepacked form of (weight, scale, offset), from the cache or packed now; undefined when the shape has
+// no prepacked form or the budget is exhausted.
+at::Tensor prepacked_weight(const at::Tensor &w, const at::Tensor &scale, const at::Tensor &offset, int64_t group,
+                            int64_t N, int64_t K)
+{
+    static std::mutex mutex;
+    // leaked on purpose: tensors must not be destroyed after the CUDA runtime at process exit
+    static auto &cache = *new std::map<PrepackKey, PrepackEntry>();
+    static size_t cached_bytes = 0;
+    size_t bytes = 0;
+    EXEC_QMM_CMD(qmm_w4a16_prepack_size, N, K, group, &bytes);
+    if (bytes == 0) {
+        return at::Tensor();
+    }
+    const at::Tensor *parts[3] = {&w, &scale, &offset};
+    const PrepackKey key{w.const_data_ptr(), scale.const_data_ptr(), op_plugin_utils::opt_ptr(offset), K, N, group,
+                         static_cast<int>(scale.scalar_type())};
+    std::lock_guard<std::mutex> lock(mutex);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        bool valid = true;
+        for (int i = 0; i < 3 && valid; ++i) {
+            if (!it->second.storages[i].has_value()) {
+                valid = !parts[i]->defined();
+                continue;
+            }
+            auto alive = it->second.storages[i]->lock();
+            valid = parts[i]->defined() && alive && alive.get() == parts[i]->storage().unsafeGetStorageImpl() &&
+                    it->second.versions[i] == version_of(*parts[i]);
+        }
+        if (valid) {
+            return it->second.packed;
+        }
+        cached_bytes -= static_cast<size_t>(it->second.packed.numel());
+        cache.erase(it);
+    }
+    if (bytes > prepack_budget_bytes()) {
+        return at::Tensor();
+    }
+    if (cached_bytes + bytes > prepack_budget_bytes()) {  // over budget: start over rather than track recency
+        cache.clear();
+        cached_bytes = 0;
+    }
+    PrepackEntry e;
+    e.packed = at::empty({static_cast<int64_t>(bytes)}, w.options().dtype(at::kByte));
+    EXEC_QMM_CMD(qmm_w4a16_prepack, static_cast<const int32_t *>(w.const_data_ptr()), N / 8, scale.const_data_ptr(),
+                 op_plugin_utils::opt_ptr(offset), op_plugin_utils::qmm_dtype(scale.scalar_type()), group, N, K,
+                 e.packed.data_ptr(), bytes, op_plugin_utils::current_stream(w));
+    for (int i = 0; i < 3; ++i) {
+        if (parts[i]->defined()) {
+            e.storages[i].emplace(
+                c10::intrusive_ptr<c10::StorageImpl>::reclaim_copy(parts[i]->storage().unsafeGetStorageImpl()));
+            e.versions[i] = version_of(*parts[i]);
+        }
+    }
+    cached_bytes += bytes;
+    at::Tensor packed = e.packed;
+    cache.emplace(key, std::move(e));
+    return packed;
+}
+
+}  // namespace
 
 at::Tensor npu_weight_quant_batchmatmul(const at::Tensor &x, const at::Tensor &weight,
                                         const at::Tensor &antiquant_scale,
@@ -73,6 +185,20 @@ at::Tensor npu_weight_quant_batchmatmul(const at::Tensor &x, const at::Tensor &w
     at::Tensor sc = antiquant_scale.contiguous();
     at::Tensor oc = offset_real.defined() ? offset_real.contiguous() : offset_real;
     at::Tensor bc = bias_real.defined() ? bias_real.contiguous() : bias_real;
+    // more than eight token rows: the tensor-memory kernel over the prepacked stream is the faster one
+    if (prepack_enabled() && M > 8 && K > 0) {
+        at::Tensor packed = prepacked_weight(wc, sc, oc, group, N, K);
+        if (packed.defined()) {
+            size_t ws_size = 0;
+            EXEC_QMM_CMD(qmm_weight_quant_batchmatmul_prepacked_workspace_size, M, N, K, &ws_size);
+            at::Tensor ws = op_plugin_utils::qmm_workspace(xc, ws_size, /*family=*/2);
+            EXEC_QMM_CMD(qmm_weight_quant_batchmatmul_prepacked, xc.const_data_ptr(),
+                         op_plugin_utils::qmm_dtype(xc.scalar_type()), K, packed.const_data_ptr(),
+                         static_cast<size_t>(packed.numel()), op_plugin_utils::opt_ptr(bc), result.data_ptr(), N, M, N,
+                         K, ws.defined() ? ws.data_ptr() : nullptr, ws_size, op_plugin_utils::current_stream(xc));
+            return result;
+        }
+    }
     size_t workspace_size = 0;
     EXEC_QMM_CMD(qmm_weight_quant_batchmatmul_workspace_size, M, N, K, group, &workspace_size);
     at::Tensor workspace = op_plugin_utils::qmm_workspace(xc, workspace_size, /*family=*/1);

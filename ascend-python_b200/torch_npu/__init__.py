@@ -43,6 +43,15 @@ def npu_dynamic_quant(input, *, smooth_scales=None):
     return _ops.npu_dynamic_quant(input, smooth_scales=smooth_scales)
 
 
+def npu_rms_norm(self, gamma, epsilon=1e-06):
+    return _ops.npu_rms_norm(self, gamma, epsilon)
+
+
+def npu_rms_norm_dynamic_quant(self, gamma, epsilon=1e-06):
+    """npu_rms_norm fused with npu_dynamic_quant: (int8 values, per-token scale, rstd)."""
+    return _ops.npu_rms_norm_dynamic_quant(self, gamma, epsilon)
+
+
 def npu_quant_matmul(x1, x2, scale, *, offset=None, pertoken_scale=None, bias=None, output_dtype=None):
     return _ops.npu_quant_matmul(x1, x2, scale, offset=offset, pertoken_scale=pertoken_scale, bias=bias,
                                  output_dtype=output_dtype)

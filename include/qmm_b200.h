@@ -76,6 +76,15 @@ QMM_API int qmm_version(void);
 QMM_API int qmm_device_status(int reset);
 
 /*
+ * Measurement utility (no counterpart in the reference): the rate at which this GPU's tensor pipe executes
+ * tcgen05.mma.kind::i8 when nothing else limits it (operands resident in shared memory, one CTA per SM,
+ * `batches` x 64 MMAs of 128 x 256 x 32 per CTA; runs on the default stream and synchronizes).  Returns
+ * int8 operations per clock and SM (from the SMs' cycle counters), TOPS over the run (CUDA events) and
+ * the SM clock the run saw.  It is the denominator of the W8A8 roofline fractions.
+ */
+QMM_API int qmm_int8_mma_peak(int batches, double *ops_per_clk_per_sm, double *tops, double *sm_mhz);
+
+/*
  * Per-token dynamic quantization (torch op `npu_dynamic_quant`; the op is not
  * in the reference snapshot, its host conventions follow
  * op_plugin/ops/base_ops/aclops/QuantizePerChannelKernelNpu.cpp:69-92).
@@ -87,6 +96,29 @@ QMM_API int qmm_device_status(int reset);
  */
 QMM_API int qmm_dynamic_quant(const void *x, int x_dtype, int64_t rows, int64_t cols, int64_t ld_x,
                               int8_t *q, int64_t ld_q, float *scale, void *stream);
+
+/*
+ * RMS normalisation (torch op `npu_rms_norm`; host function
+ * op_plugin/ops/base_ops/opapi/RmsNormKernelOpApi.cpp:24-35, numpy golden
+ * test/test_custom_ops/test_npu_rms_norm.py:10-18):
+ *   variance[r] = mean_c x[r,c]^2;  rstd[r] = 1 / sqrt(variance[r] + epsilon);
+ *   y[r,c] = (x[r,c] * rstd[r]) * gamma[c]        fp32, one rounding per operation, y rounded to x's dtype
+ * x, y: [rows, cols] of x_dtype (BF16, F16 or F32), row strides ld_x / ld_y; gamma: [cols] of x_dtype;
+ * rstd: [rows] fp32.
+ */
+QMM_API int qmm_rms_norm(const void *x, int x_dtype, int64_t rows, int64_t cols, int64_t ld_x, const void *gamma,
+                         double epsilon, void *y, int64_t ld_y, float *rstd, void *stream);
+
+/*
+ * qmm_rms_norm followed by qmm_dynamic_quant of its output, in one pass over HBM (torch op
+ * `npu_rms_norm_dynamic_quant`, which has no counterpart in the reference: it fuses the reference's
+ * npu_rms_norm, RmsNormKernelOpApi.cpp:24-35, with the quantization step that consumes it).  q and scale
+ * are bit-identical to qmm_dynamic_quant(qmm_rms_norm(x)): the normalised row is rounded to x_dtype
+ * (BF16 or F16) in registers before its absmax is taken.
+ */
+QMM_API int qmm_rms_norm_dynamic_quant(const void *x, int x_dtype, int64_t rows, int64_t cols, int64_t ld_x,
+                                       const void *gamma, double epsilon, int8_t *q, int64_t ld_q, float *scale,
+                                       float *rstd, void *stream);
 
 /*
  * Bytes of scratch memory qmm_quant_matmul needs for a problem (first phase
@@ -135,8 +167,9 @@ QMM_API int qmm_quant_matmul(const int8_t *x1, int64_t ld_x1, const int8_t *x2, 
  *     (cudaGetSymbolAddress); make that first call before any stream capture.
  *   - all calls on a device share the one array: calls that may overlap on the
  *     GPU (different streams without ordering) race on it; keep them ordered.
- *   - bounded device-side waits that give up are not reported by
- *     qmm_device_status on this path.
+ *   - a bounded device-side wait that gives up on this path is recorded in a status word
+ *     inside the library image, read with qmm_noalloc_status (qmm_device_status reads
+ *     allocated host memory, which this path never creates).
  */
 #define QMM_NOALLOC_SCRATCH_BYTES (16u << 20)
 QMM_API int qmm_quant_matmul_decode_noalloc(const int8_t *x1, int64_t ld_x1, const int8_t *x2,
@@ -144,6 +177,9 @@ QMM_API int qmm_quant_matmul_decode_noalloc(const int8_t *x1, int64_t ld_x1, con
                                             int64_t scale_len, const float *pertoken_scale, const void *bias,
                                             int bias_dtype, void *out, int out_dtype, int64_t ld_out, int64_t M,
                                             int64_t N, int64_t K, void *stream);
+/* Status word of the entry point above on the current device (0 = no wait gave up, -1 = the read failed);
+ * synchronizes with the device; `reset` != 0 clears it.  Allocates nothing. */
+QMM_API int qmm_noalloc_status(int reset);
 
 /*
  * W4A16 matmul (torch op `npu_weight_quant_batchmatmul`; host conventions as
@@ -169,6 +205,34 @@ QMM_API int qmm_weight_quant_batchmatmul(const void *x, int x_dtype, int64_t ld_
                                          void *out, int64_t ld_out, int64_t M, int64_t N, int64_t K,
                                          void *workspace, size_t workspace_bytes, void *stream);
 
+/*
+ * Prepacked W4A16 weights.  The reference keeps matmul operands in a private device format and
+ * casts to and from the plain layout around the matmul (ND <-> FRACTAL_NZ,
+ * op_plugin/ops/base_ops/aclops/MmKernelNpu.cpp:80-94, :301-316); this is the same step for the
+ * int4 weights of npu_weight_quant_batchmatmul.  qmm_w4a16_prepack rewrites weight [K, N/8] with
+ * its antiquant scale and offset ONCE into a k-major stream (128 columns x 128 k per block, scale
+ * and offset*scale of the block's group behind its nibbles); qmm_weight_quant_batchmatmul_prepacked
+ * then computes the same product as qmm_weight_quant_batchmatmul from that buffer alone, with the
+ * weight W = fma(w, scale, offset*scale) rounded once to the activation dtype before the
+ * tensor-core product (fp32 accumulation).
+ *   - supported: N % 8 == 0, K % 128 == 0, group a multiple of 128 that divides K (group <= 0 means K);
+ *     qmm_w4a16_prepack_size returns 0 bytes for anything else and the stock entry point remains.
+ *   - sdtype (BF16/F16) is the dtype of scale and offset and must equal the x_dtype used later.
+ *   - packed: 16-byte aligned, at least qmm_w4a16_prepack_size bytes.
+ *   - qmm_w4a16_unpack_weight restores the stock int32 [K, N/8] words exactly.
+ *   - workspace of the matmul: 256-byte aligned, zero-filled before its first use only.
+ */
+QMM_API int qmm_w4a16_prepack_size(int64_t N, int64_t K, int64_t group, size_t *bytes);
+QMM_API int qmm_w4a16_prepack(const int32_t *weight, int64_t ld_w, const void *antiquant_scale,
+                              const void *antiquant_offset, int sdtype, int64_t group, int64_t N, int64_t K,
+                              void *packed, size_t packed_bytes, void *stream);
+QMM_API int qmm_w4a16_unpack_weight(const void *packed, int64_t N, int64_t K, int32_t *weight, int64_t ld_w,
+                                    void *stream);
+QMM_API int qmm_weight_quant_batchmatmul_prepacked_workspace_size(int64_t M, int64_t N, int64_t K, size_t *bytes);
+QMM_API int qmm_weight_quant_batchmatmul_prepacked(const void *x, int x_dtype, int64_t ld_x, const void *packed,
+                                                   size_t packed_bytes, const void *bias, void *out,
+                                                   int64_t ld_out, int64_t M, int64_t N, int64_t K,
+                                                   void *workspace, size_t workspace_bytes, void *stream);
 
 /*
  * Communicator registry.  The reference passes a communicator NAME into its
@@ -184,6 +248,10 @@ QMM_API int qmm_comm_init_rank(const char *name, const void *id, int nranks, int
 QMM_API int qmm_comm_register(const char *name, void *nccl_comm, int nranks, int rank);
 QMM_API int qmm_comm_info(const char *name, int *nranks, int *rank);
 QMM_API int qmm_comm_destroy(const char *name);
+/* Calls of qmm_mm_all_reduce made through the communicator so far, by the path their allreduce took:
+ * the library's own kernel over peer memory (and, of those, calls whose matmul pushed its output tiles to
+ * the owning ranks itself), or NCCL.  Any pointer may be NULL.  No counterpart in the reference. */
+QMM_API int qmm_comm_stats(const char *name, int64_t *peer_calls, int64_t *peer_pushed_calls, int64_t *nccl_calls);
 
 /* Peer memory for the allreduce of qmm_mm_all_reduce (no counterpart in the reference: its device
  * library owns the communication buffers behind the communicator name,
@@ -194,7 +262,11 @@ QMM_API int qmm_comm_destroy(const char *name);
  * multicast object - the multicast address (else NULL).  qmm_comm_peer_memory_size gives the size an
  * allreduce of [M][N] 16-bit values needs.  While regions are attached and large enough, calls
  * with comm_turn == 0 reduce and gather through NVLink loads in one kernel per rank instead of
- * NCCL; the environment variable QMM_ALLREDUCE=nccl switches that off.  bytes == 0 detaches. */
+ * NCCL; the environment variable QMM_ALLREDUCE=nccl switches that off (set it on every rank or on
+ * none).  The choice depends only on M, N, comm_turn and the attached size, which all ranks share; on
+ * that path `out` must be 16-byte aligned and the stream must not be capturing (both are errors, not a
+ * switch to NCCL that the other ranks would not follow).  Calls of different shapes may follow one
+ * another without synchronisation in between.  bytes == 0 detaches. */
 QMM_API int qmm_comm_peer_memory_size(int64_t M, int64_t N, int nranks, size_t *bytes);
 QMM_API int qmm_comm_attach_peer_memory(const char *name, const void *const *regions, const void *multicast,
                                         size_t bytes);

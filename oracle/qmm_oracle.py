@@ -22,7 +22,8 @@ Every choice the reference leaves open is fixed here, once:
 
 * dynamic quant: ``scale = amax / 127`` and ``q = rint(x / scale)`` with true
   IEEE fp32 divisions, round-half-to-even, clamp to [-128, 127]; a row whose
-  amax is 0 gets scale 0 and q 0.
+  amax is 0 gets scale 0 and q 0; amax propagates NaN and Inf into the scale,
+  and a quotient that is NaN quantizes to 0.
 * quant matmul: exact int32 accumulation; epilogue in fp32, one rounding per
   operation, in the order ``float(acc) * scale[n] * pertoken[m] + bias[n]``,
   then one round-to-nearest-even conversion to bf16/f16.  With
@@ -91,9 +92,43 @@ def dynamic_quant(x):
     safe = np.where(scale == 0, np.float32(1.0), scale).astype(np.float32)
     with np.errstate(all="ignore"):
         t = (xf / safe[:, None]).astype(np.float32)
+    t = np.where(np.isnan(t), np.float32(0), t)  # Inf/Inf or anything/NaN: pinned to 0
     q = np.clip(np.rint(t), -128, 127)
     q = np.where(scale[:, None] == 0, 0, q).astype(np.int8)
     return torch.from_numpy(q.reshape(shape)), torch.from_numpy(scale.reshape(shape[:-1]))
+
+
+# ---------------------------------------------------------------------------
+# npu_rms_norm (+ the dynamic quantization that follows it in a decoder block)
+# ---------------------------------------------------------------------------
+
+
+def rms_norm(x, gamma, epsilon: float = 1e-6):
+    """RMS normalisation; returns (y in x's dtype, rstd fp32 of shape x.shape[:-1] + (1,)).
+
+    Restates the numpy golden of test/test_custom_ops/test_npu_rms_norm.py:10-18 operation by
+    operation in float32 (``variance = mean(x**2, -1)``, ``std = sqrt(variance + eps)``,
+    ``rstd = 1/std``, ``y = (x*rstd)*gamma``); 16-bit inputs are widened exactly first and y is
+    rounded once to the input dtype.  tests/golden/rms_norm_reference.npz holds outputs of the
+    reference's own function on seeded inputs (made by tests/golden/make_rms_norm_golden.py), and
+    tests/test_oracle.py checks this function against them bit for bit: this oracle is pinned.
+    """
+    dtype = x.dtype if isinstance(x, torch.Tensor) else torch.float32
+    xf, gf = _f32(x), _f32(gamma)
+    variance = np.mean(np.power(xf, 2), axis=-1, keepdims=True)
+    std = np.sqrt(variance + np.float32(epsilon))
+    rstd = (1 / std).astype(np.float32)
+    y = ((xf * rstd).astype(np.float32) * gf).astype(np.float32)
+    return _round_to(y, dtype), torch.from_numpy(rstd)
+
+
+def rms_norm_dynamic_quant(x, gamma, epsilon: float = 1e-6):
+    """dynamic_quant(rms_norm(x)[0]): (q int8, scale fp32, rstd fp32) -- the composition the fused kernel
+    must reproduce (the int8 values and scales bit for bit GIVEN the same y; y itself to the tolerance of
+    rms_norm, whose row sum the device takes in another order)."""
+    y, rstd = rms_norm(x, gamma, epsilon)
+    q, scale = dynamic_quant(y)
+    return q, scale, rstd
 
 
 # ---------------------------------------------------------------------------

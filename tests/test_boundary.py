@@ -46,13 +46,14 @@ def test_validation_needs_no_gpu(capi):
     rc = lib.qmm_mm_all_reduce(None, 8, None, 8, 1, None, 8, None, None, -1, None, 0, 8, 4, 8, 8, b"c", b"max", 0,
                                None, 0, None)
     assert rc == 1 and b"reduce_op" in lib.qmm_last_error()
-    # peer memory of the allreduce: the size is plain arithmetic (64 KiB of flags, the partials as
-    # [ranks][rows per rank rounded up to 32][N], the reduced [M][N], 16-bit elements, 256-byte rounding)
+    # peer memory of the allreduce: the size is plain arithmetic (64 KiB of flags + two halves of equal size,
+    # each large enough for the partials as [ranks][rows per rank rounded up to 32][N] and for the reduced
+    # [M][N]; 16-bit elements, 256-byte rounding)
     need = ctypes.c_size_t(0)
     assert lib.qmm_comm_peer_memory_size(4096, 8192, 8, ctypes.byref(need)) == 0
     assert need.value == 65536 + 2 * 4096 * 8192 * 2
     assert lib.qmm_comm_peer_memory_size(1000, 768, 3, ctypes.byref(need)) == 0
-    assert need.value == 65536 + 3 * 352 * 768 * 2 + 1000 * 768 * 2
+    assert need.value == 65536 + 2 * max(3 * 352 * 768 * 2, 1000 * 768 * 2)
     assert lib.qmm_comm_peer_memory_size(-1, 8, 2, ctypes.byref(need)) == 1
     regions = (ctypes.c_void_p * 2)(None, None)
     rc = lib.qmm_comm_attach_peer_memory(b"no-such-comm", regions, None, 1 << 20)
@@ -75,6 +76,9 @@ def test_ops_registered_with_reference_signatures(pkg):
     assert "str hcom" in str(ops.npu_mm_all_reduce_base.default._schema)
     assert 'str reduce_op="sum"' in str(ops.npu_mm_all_reduce_base.default._schema)
     assert "int antiquant_group_size=0" in str(ops.npu_weight_quant_batchmatmul.default._schema)
+    # the reference's own entry, verbatim (op_plugin/config/v2r1/op_plugin_functions.yaml:2113)
+    assert str(ops.npu_rms_norm.default._schema) == \
+        "npu::npu_rms_norm(Tensor self, Tensor gamma, float epsilon=9.9999999999999995e-07) -> (Tensor, Tensor)"
     # CUDA is the only backend: a CPU tensor has nowhere to go
     with pytest.raises((RuntimeError, NotImplementedError)):
         ops.npu_dynamic_quant(torch.zeros(2, 8, dtype=torch.bfloat16))
@@ -112,8 +116,8 @@ def test_codegen_declarations(tmp_path):
     with pytest.raises(ValueError):
         gen.parse_schema("f(Dimname d) -> Tensor", "op_api")
     ops = gen.run(PKG_DIR / "op_plugin" / "config" / "op_plugin_functions.yaml", tmp_path)
-    assert [o.name for o in ops] == ["npu_dynamic_quant", "npu_quant_matmul", "npu_weight_quant_batchmatmul",
-                                     "npu_mm_all_reduce_base"]
+    assert [o.name for o in ops][:6] == ["npu_dynamic_quant", "npu_quant_matmul", "npu_weight_quant_batchmatmul",
+                                         "npu_mm_all_reduce_base", "npu_rms_norm", "npu_rms_norm_dynamic_quant"]
     lib_cpp = (tmp_path / "TorchLibrary.cpp").read_text()
     assert "TORCH_LIBRARY_FRAGMENT(npu, m)" in lib_cpp and "TORCH_LIBRARY_IMPL(npu, CUDA, m)" in lib_cpp
     assert "return op_api::npu_quant_matmul(x1, x2, scale, offset, pertoken_scale, bias, output_dtype);" in \

@@ -126,3 +126,23 @@ def test_full_size_properties(capi, oracle, dev):
         err = (x.float() - q.float() * s[:, None]).abs()
         assert torch.all(err <= s[:, None] * 0.50002)  # half a step + fp32 rounding of x/s and q*s
         del x, err
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("cols", [8, 1024, 4096 + 8, 33])
+def test_non_finite_rows(capi, oracle, dev, dtype, cols):
+    """A row with an infinity: infinite scale, every element 0.  A row with a NaN: NaN scale, every element 0.
+    Neighbouring rows are untouched (both the vector kernel and the any-alignment kernel)."""
+    g = torch.Generator().manual_seed(cols)
+    x = torch.randn((6, cols), generator=g).to(dtype)
+    x[1, cols // 2] = float("inf")
+    x[3, cols - 1] = float("nan")
+    x[4, 0] = float("-inf")
+    q_ref, s_ref = oracle.dynamic_quant(x)
+    q, s = capi.dynamic_quant(x.to(dev))
+    assert torch.equal(q.cpu(), q_ref)
+    s, s_ref = s.cpu(), s_ref
+    assert torch.isnan(s[3]) and torch.isnan(s_ref[3])
+    keep = [0, 1, 2, 4, 5]
+    assert torch.equal(s[keep], s_ref[keep]) and torch.isinf(s[1]) and torch.isinf(s[4])
+    assert not q[1].any() and not q[3].any() and not q[4].any()

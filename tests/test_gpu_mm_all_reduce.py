@@ -83,6 +83,19 @@ def test_missing_rank_times_out(capi, oracle, dev):
         capi.check(lib.qmm_comm_destroy(b"half"), "qmm_comm_destroy")
 
 
+def _sample_rows(M, K, N):
+    """Rows compared with the oracle: all of them, or 64 evenly spaced ones for the full-size configuration
+    (whose CPU oracle would take minutes)."""
+    return None if M * K * N <= 2 ** 36 else torch.arange(0, M, M // 64)
+
+
+def _digest(t):
+    """Order-dependent 64-bit checksum of a tensor's bits (for cross-rank identity of full outputs)."""
+    v = t.contiguous().view(torch.int16).to(torch.int64)
+    w = torch.arange(1, v.numel() + 1, device=v.device, dtype=torch.int64).view(v.shape)
+    return int((v * w).sum().item())
+
+
 def _rank_main(rank, world, port, shapes, c2p):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -105,7 +118,30 @@ def _rank_main(rank, world, port, shapes, c2p):
             y = torch_npu.npu_mm_all_reduce_base(q, ws.contiguous().to(dev), hcom, reduce_op="sum", bias=bias.to(dev),
                                                  dequant_scale=scale.to(dev), pertoken_scale=s, comm_turn=turn)
             torch.cuda.synchronize()
-            c2p.put((rank, (M, K, N, turn), y.cpu(), q.cpu(), s.cpu()))
+            rows = _sample_rows(M, K, N)
+            if rows is None:
+                c2p.put((rank, (M, K, N, turn), y.cpu(), q.cpu(), s.cpu(), _digest(y)))
+            else:
+                c2p.put((rank, (M, K, N, turn), y[rows].cpu(), q[rows].cpu(), s[rows].cpu(), _digest(y)))
+        # Two calls of different shapes back to back, no host synchronisation in between: the second call's
+        # partial area must not land where the first call's reduced rows are still being read by a peer.
+        chain = [(256, 1024, 512), (2048, 4096, 1024)]
+        outs = []
+        ins = []
+        for (M, K, N) in chain:
+            x, w, scale, bias = O.make_w8a8_inputs(M, K, N, seed=M + K + N)
+            xs, ws = shard_row_parallel(x, w, world, rank)
+            ins.append((xs.contiguous().to(dev), ws.contiguous().to(dev), scale.to(dev), bias.to(dev)))
+        torch.cuda.synchronize()
+        for _ in range(3):
+            for (xd, wd, sd, bd) in ins:
+                q, s = torch_npu.npu_dynamic_quant(xd)
+                outs.append(torch_npu.npu_mm_all_reduce_base(q, wd, hcom, reduce_op="sum", bias=bd, dequant_scale=sd,
+                                                             pertoken_scale=s))
+        torch.cuda.synchronize()
+        for i, y in enumerate(outs):
+            M, K, N = chain[i % 2]
+            c2p.put((rank, ("chain", i, M, K, N), y.cpu(), None, None, _digest(y)))
         dist.barrier()
         torch_npu.destroy_comm(hcom)
     finally:
@@ -125,6 +161,8 @@ def test_multi_rank(oracle, pkg, world, path):
     # the last shape needs larger peer regions than the first ones allocated: the regions are re-made
     shapes = [(256, 1024, 512, 0), (2048, 4096, 1024, 2), (1000, 2048, 768, 3), (1000, 2048, 768, 0),
               (2048, 4096, 1024, 0), (3, 512, 264, 0), (4096, 512, 4352, 0)]
+    if path == "peer":
+        shapes.append((4096, 28672, 8192, 0))  # the row-parallel benchmark configuration itself, at full size
     ctx = mp.get_context("spawn")
     c2p = ctx.Queue()
     port = 29700 + os.getpid() % 1000
@@ -137,9 +175,9 @@ def test_multi_rank(oracle, pkg, world, path):
         for p in procs:
             p.start()
         results = {}
-        for _ in range(world * len(shapes)):
-            rank, key, y, q, s = c2p.get(timeout=600)
-            results[(rank, key)] = (y, q, s)
+        for _ in range(world * (len(shapes) + 6)):
+            rank, key, y, q, s, digest = c2p.get(timeout=900)
+            results[(rank, key)] = (y, q, s, digest)
         for p in procs:
             p.join(timeout=120)
             assert p.exitcode == 0
@@ -149,6 +187,9 @@ def test_multi_rank(oracle, pkg, world, path):
     for key in shapes:
         M, K, N, _ = key
         x, w, scale, bias = oracle.make_w8a8_inputs(M, K, N, seed=M + K + N)
+        rows = _sample_rows(M, K, N)
+        if rows is not None:
+            x = x[rows]
         q_list = [results[(r, key)][1] for r in range(world)]
         s_list = [results[(r, key)][2] for r in range(world)]
         w_list = [shard_row_parallel(x, w, world, r)[1] for r in range(world)]
@@ -156,6 +197,7 @@ def test_multi_rank(oracle, pkg, world, path):
         for r in range(world):
             q_ref, s_ref = oracle.dynamic_quant(shard_row_parallel(x, w, world, r)[0].contiguous())
             assert torch.equal(q_list[r], q_ref) and torch.equal(s_list[r], s_ref)
+            assert results[(r, key)][3] == results[(0, key)][3], f"rank {r} holds another result than rank 0: {key}"
         total, rounded = oracle.mm_all_reduce(q_list, w_list, scale, s_list, bias=bias, output_dtype=torch.bfloat16)
         mag = sum(np.abs(oracle.quant_matmul(q_list[r], w_list[r], scale, pertoken_scale=s_list[r],
                                               output_dtype=torch.bfloat16).float().numpy()) for r in range(world))
@@ -167,3 +209,21 @@ def test_multi_rank(oracle, pkg, world, path):
             # the library's own kernel adds the ranks' rounded partials in fp32 in rank order and rounds once,
             # which is the oracle's order: bit-exact, not just within the tolerance
             assert torch.equal(results[(0, key)][0].view(torch.int16), rounded.view(torch.int16)), f"shape {key}"
+    # the back-to-back calls of alternating shapes: every repetition equals the oracle's rounded sum on every rank
+    for i in range(6):
+        M, K, N = [(256, 1024, 512), (2048, 4096, 1024)][i % 2]
+        key = ("chain", i, M, K, N)
+        x, w, scale, bias = oracle.make_w8a8_inputs(M, K, N, seed=M + K + N)
+        q_list, s_list, w_list = [], [], []
+        for r in range(world):
+            xs, ws = shard_row_parallel(x, w, world, r)
+            qr, sr = oracle.dynamic_quant(xs.contiguous())
+            q_list.append(qr), s_list.append(sr), w_list.append(ws)
+        total, rounded = oracle.mm_all_reduce(q_list, w_list, scale, s_list, bias=bias, output_dtype=torch.bfloat16)
+        for r in range(world):
+            y = results[(r, key)][0]
+            if path == "peer":
+                assert torch.equal(y.view(torch.int16), rounded.view(torch.int16)), f"rank {r} chained call {i}"
+            else:
+                assert np.all(np.abs(y.float().numpy() - total) <= 1e-2 * np.abs(total) + 2e-2 * np.abs(total).max())
+            assert results[(r, key)][3] == results[(0, key)][3]

@@ -215,3 +215,37 @@ def test_ulp_distance(oracle):
     a = torch.tensor([1.0, -1.0, 0.0, 2.0], dtype=torch.bfloat16)
     b = torch.tensor([1.0078125, -1.0078125, -0.0, 2.0], dtype=torch.bfloat16)
     assert oracle.bf16_ulp_distance(a, b).tolist() == [1, 1, 0, 0]
+
+
+def test_rms_norm_pinned_to_reference_golden():
+    """oracle.rms_norm against outputs of the reference's own numpy golden (executed from the reference's
+    test file by tests/golden/make_rms_norm_golden.py): bit for bit."""
+    from oracle import qmm_oracle as O
+
+    g = np.load(GOLDEN / "rms_norm_reference.npz")
+    for name in ("a", "b", "c"):
+        y, rstd = O.rms_norm(torch.from_numpy(g[f"{name}_x"]), torch.from_numpy(g[f"{name}_gamma"]), 1e-6)
+        assert np.array_equal(y.numpy(), g[f"{name}_y"]) and np.array_equal(rstd.numpy(), g[f"{name}_rstd"])
+
+
+def test_rms_norm_dynamic_quant_composition():
+    from oracle import qmm_oracle as O
+
+    x = (torch.randn((6, 384), generator=torch.Generator().manual_seed(3)) * 2).to(torch.bfloat16)
+    gamma = (torch.rand(384, generator=torch.Generator().manual_seed(4)) + 0.5).to(torch.bfloat16)
+    q, s, rstd = O.rms_norm_dynamic_quant(x, gamma)
+    y, rstd2 = O.rms_norm(x, gamma)
+    q2, s2 = O.dynamic_quant(y)
+    assert y.dtype == torch.bfloat16 and torch.equal(q, q2) and torch.equal(s, s2) and torch.equal(rstd, rstd2)
+    assert rstd.shape == (6, 1)
+
+
+def test_dynamic_quant_non_finite_rows():
+    """Pinned choices: an infinite element gives an infinite scale (finite elements -> 0, the infinity itself
+    -> 0 because Inf/Inf is NaN); a NaN gives a NaN scale and an all-zero row."""
+    from oracle import qmm_oracle as O
+
+    x = torch.tensor([[1.0, -2.0, float("inf"), 4.0], [1.0, float("nan"), -3.0, 0.5], [1.0, 2.0, -4.0, 0.0]]).to(torch.bfloat16)
+    q, s = O.dynamic_quant(x)
+    assert torch.isinf(s[0]) and torch.isnan(s[1]) and s[2].item() == np.float32(4.0) / np.float32(127.0)
+    assert q[0].tolist() == [0, 0, 0, 0] and q[1].tolist() == [0, 0, 0, 0] and q[2].tolist() == [32, 64, -127, 0]

@@ -78,3 +78,31 @@ def test_sizes_beyond_the_builtin_scratch_are_refused(capi, dev):
                                              capi.DTYPE_NONE, out2.data_ptr(), capi.DTYPE_I32, N, 256, N, K,
                                              torch.cuda.current_stream().cuda_stream)
     assert rc == 2 and b"1 <= M <= 128" in lib.qmm_last_error()
+
+
+def test_allocates_nothing_and_reports_timeouts_in_its_own_word(capi, dev):
+    """The claim in the name: the device's free memory is the same before and after a call (the first call on
+    a device looked the array's address up earlier in this file), and the entry point's own status word - the
+    one a timed-out wait would mark - reads 0 after correct runs."""
+    M, K, N = 16, 2048, 4096
+    a = torch.randint(-127, 128, (M, K), device=dev, dtype=torch.int8)
+    w = torch.randint(-127, 128, (K, N), device=dev, dtype=torch.int8)
+    out = torch.empty((M, N), dtype=torch.int32, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    lib = capi.lib()
+
+    def call():
+        rc = lib.qmm_quant_matmul_decode_noalloc(a.data_ptr(), K, w.data_ptr(), N, 1, None, 0, None, None,
+                                                 capi.DTYPE_NONE, out.data_ptr(), capi.DTYPE_I32, N, M, N, K, stream)
+        capi.check(rc, "qmm_quant_matmul_decode_noalloc")
+
+    call()  # set-up, if this test runs alone
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, f"device free memory changed by {free_before - free_after} bytes"
+    assert torch.equal(out, capi.quant_matmul(a, w, None, output_dtype=torch.int32, algo=capi.ALGO_STREAMK))
+    assert lib.qmm_noalloc_status(0) == 0
