@@ -432,6 +432,29 @@ static __device__ __align__(256) uint8_t g_noalloc_scratch[QMM_NOALLOC_SCRATCH_B
 // Where a kernel launched through this entry point records a bounded wait that gave up (the process-wide
 // status word of the other entry points lives in allocated host memory, which this path must not create).
 static __device__ uint32_t g_noalloc_status;
+// Codes already acted upon by noalloc_prepare_kernel (kept so that the host can still read them).
+static __device__ uint32_t g_noalloc_status_reported;
+
+// What must start at zero: the partial sums and tile counters.  The stream-K kernel hands the array back
+// zeroed (every tile's last arriver clears what the tile used), so in the normal case there is nothing to do
+// and a memset of up to 16 MiB per call (74 us at M = 128, N = 28672) would be wasted.  Only a call that was cut
+// short - a bounded wait gave up, which the kernel records in g_noalloc_status - can leave sums behind; this
+// one-CTA kernel, launched in front of every call, clears the whole array when the status word is set, and
+// moves the code to a second word for the host to read.  The library loader zero-fills the array, so the first
+// call needs no clearing either.
+__global__ void __launch_bounds__(1024) noalloc_prepare_kernel() {
+    __shared__ uint32_t code;
+    if (threadIdx.x == 0) code = g_noalloc_status;
+    __syncthreads();
+    if (code == 0) return;
+    uint4 *p = reinterpret_cast<uint4 *>(g_noalloc_scratch);
+    for (uint32_t i = threadIdx.x; i < QMM_NOALLOC_SCRATCH_BYTES / 16; i += blockDim.x) p[i] = make_uint4(0, 0, 0, 0);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (code > g_noalloc_status_reported) g_noalloc_status_reported = code;
+        g_noalloc_status = 0;
+    }
+}
 
 constexpr int kMaxDevices = 64;
 std::mutex g_noalloc_mutex;
@@ -502,9 +525,11 @@ extern "C" int qmm_quant_matmul_decode_noalloc(const int8_t *x1, int64_t ld_x1, 
     rc = noalloc_scratch_address(&scratch, &status);
     if (rc != QMM_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // The array keeps whatever the previous call left (zeros, unless that call was
-    // cut short): the partial sums and counters of this problem start from zero.
-    QMM_CUDA_OK(cudaMemsetAsync(scratch, 0, need, s));
+    // The array keeps whatever the previous call left: zeros, unless that call was cut short, in which case
+    // the prepare kernel clears it (device code names the array directly; only the launch below needs the
+    // address that was looked up).
+    noalloc_prepare_kernel<<<1, 1024, 0, s>>>();
+    QMM_CUDA_OK(cudaGetLastError());
     EpilogueParams ep;
     ep.scale = scale;
     ep.pertoken_scale = (out_dtype == QMM_DTYPE_I32) ? nullptr : pertoken_scale;
@@ -527,14 +552,17 @@ extern "C" int qmm_quant_matmul_decode_noalloc(const int8_t *x1, int64_t ld_x1, 
 
 extern "C" int qmm_noalloc_status(int reset) {
     using namespace qmm;
-    uint32_t v = 0;
-    if (cudaMemcpyFromSymbol(&v, g_noalloc_status, sizeof(v)) != cudaSuccess) {
+    // the live word (a call was cut short and no later call has cleaned up yet) or the word of codes already
+    // cleaned up after; only the second one is cleared here, the first one belongs to the prepare kernel
+    uint32_t live = 0, reported = 0;
+    if (cudaMemcpyFromSymbol(&live, g_noalloc_status, sizeof(live)) != cudaSuccess ||
+        cudaMemcpyFromSymbol(&reported, g_noalloc_status_reported, sizeof(reported)) != cudaSuccess) {
         (void)cudaGetLastError();
         return -1;
     }
-    if (reset && v != 0) {
+    if (reset && reported != 0) {
         const uint32_t zero = 0;
-        (void)cudaMemcpyToSymbol(g_noalloc_status, &zero, sizeof(zero));
+        (void)cudaMemcpyToSymbol(g_noalloc_status_reported, &zero, sizeof(zero));
     }
-    return static_cast<int>(v);
+    return static_cast<int>(live > reported ? live : reported);
 }

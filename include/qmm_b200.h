@@ -167,6 +167,9 @@ QMM_API int qmm_quant_matmul(const int8_t *x1, int64_t ld_x1, const int8_t *x2, 
  *     (cudaGetSymbolAddress); make that first call before any stream capture.
  *   - all calls on a device share the one array: calls that may overlap on the
  *     GPU (different streams without ordering) race on it; keep them ordered.
+ *   - the array keeps what the last call left.  The kernel hands it back zeroed, which
+ *     is what the next call needs; a small kernel in front of every call clears it
+ *     after a call that was cut short (no per-call memset of the 16 MiB).
  *   - a bounded device-side wait that gives up on this path is recorded in a status word
  *     inside the library image, read with qmm_noalloc_status (qmm_device_status reads
  *     allocated host memory, which this path never creates).
@@ -178,7 +181,7 @@ QMM_API int qmm_quant_matmul_decode_noalloc(const int8_t *x1, int64_t ld_x1, con
                                             int bias_dtype, void *out, int out_dtype, int64_t ld_out, int64_t M,
                                             int64_t N, int64_t K, void *stream);
 /* Status word of the entry point above on the current device (0 = no wait gave up, -1 = the read failed);
- * synchronizes with the device; `reset` != 0 clears it.  Allocates nothing. */
+ * synchronizes with the device; `reset` != 0 clears the codes whose clean-up has already run.  Allocates nothing. */
 QMM_API int qmm_noalloc_status(int reset);
 
 /*
