@@ -32,6 +32,8 @@ EXPORTED_SYMBOLS = (
     "qmm_w4a16_prepack_size", "qmm_w4a16_prepack", "qmm_w4a16_unpack_weight",
     "qmm_weight_quant_batchmatmul_prepacked_workspace_size", "qmm_weight_quant_batchmatmul_prepacked",
     "qmm_rms_norm", "qmm_rms_norm_dynamic_quant", "qmm_comm_stats", "qmm_int8_mma_peak", "qmm_noalloc_status",
+    "qmm_mm_reduce_scatter_workspace_size", "qmm_mm_reduce_scatter", "qmm_all_gather_mm_workspace_size",
+    "qmm_all_gather_mm",
 )
 NOALLOC_SCRATCH_BYTES = 16 << 20
 
@@ -116,6 +118,18 @@ def lib() -> ctypes.CDLL:
         L.qmm_int8_mma_peak.restype = c.c_int
         L.qmm_noalloc_status.argtypes = [c.c_int]
         L.qmm_noalloc_status.restype = c.c_int
+        L.qmm_mm_reduce_scatter_workspace_size.argtypes = [c.c_int64, c.c_int64, c.c_int64, c.c_int,
+                                                           c.POINTER(c.c_size_t)]
+        L.qmm_mm_reduce_scatter.argtypes = [c.c_void_p, c.c_int, c.c_int64, c.c_void_p, c.c_int64, c.c_int64,
+                                            c.c_void_p, c.c_void_p, c.c_int64, c.c_int64, c.c_int64, c.c_int64,
+                                            c.c_char_p, c.c_char_p, c.c_int64, c.c_void_p, c.c_size_t, c.c_void_p]
+        L.qmm_all_gather_mm_workspace_size.argtypes = [c.c_int64, c.c_int64, c.c_int64, c.c_int, c.POINTER(c.c_size_t)]
+        L.qmm_all_gather_mm.argtypes = [c.c_void_p, c.c_int, c.c_int64, c.c_void_p, c.c_int64, c.c_int64, c.c_void_p,
+                                        c.c_void_p, c.c_int64, c.c_void_p, c.c_int64, c.c_int64, c.c_int64, c.c_int64,
+                                        c.c_char_p, c.c_int64, c.c_int64, c.c_void_p, c.c_size_t, c.c_void_p]
+        for name in ("qmm_mm_reduce_scatter_workspace_size", "qmm_mm_reduce_scatter",
+                     "qmm_all_gather_mm_workspace_size", "qmm_all_gather_mm"):
+            getattr(L, name).restype = c.c_int
         L.qmm_comm_unique_id.argtypes = [c.c_void_p]
         L.qmm_comm_init_rank.argtypes = [c.c_char_p, c.c_void_p, c.c_int, c.c_int]
         L.qmm_comm_register.argtypes = [c.c_char_p, c.c_void_p, c.c_int, c.c_int]

@@ -25,7 +25,9 @@
 #include <mutex>
 #include <vector>
 
+#include "dense_gemm.cuh"
 #include "peer_all_reduce.cuh"
+#include "peer_scatter_gather.cuh"
 #include "qmm_common.cuh"
 #include "w8a8_epilogue.cuh"
 
@@ -49,6 +51,9 @@ struct NcclApi {
     ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
     ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t,
                               cudaStream_t) = nullptr;
+    ncclResult_t (*ReduceScatter)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t,
+                                  cudaStream_t) = nullptr;
+    ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t *) = nullptr;
     const char *(*GetErrorString)(ncclResult_t) = nullptr;
     std::string error;
@@ -83,6 +88,8 @@ NcclApi &nccl() {
         api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(sym("ncclCommDestroy"));
         api.CommAbort = reinterpret_cast<decltype(api.CommAbort)>(sym("ncclCommAbort"));
         api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(sym("ncclAllReduce"));
+        api.ReduceScatter = reinterpret_cast<decltype(api.ReduceScatter)>(sym("ncclReduceScatter"));
+        api.AllGather = reinterpret_cast<decltype(api.AllGather)>(sym("ncclAllGather"));
         api.CommGetAsyncError = reinterpret_cast<decltype(api.CommGetAsyncError)>(sym("ncclCommGetAsyncError"));
         api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(sym("ncclGetErrorString"));
     });
@@ -122,7 +129,9 @@ struct PeerMem {
     uint8_t *base[kPeerMaxRanks] = {};
     uint8_t *mc_base = nullptr;  // the same regions through the NVLink multicast mapping, if there is one
     size_t bytes = 0;     // size of every region
-    uint32_t epoch = 0;   // number of allreduce calls made through the regions
+    uint32_t epoch = 0;   // number of collective calls made through the regions
+    uint32_t rs_calls = 0;  // reduce-scatter / all-gather calls so far (targets of their CTA counters)
+    uint32_t ag_calls = 0;
 };
 
 struct Comm {
@@ -587,4 +596,296 @@ extern "C" int qmm_mm_all_reduce(const int8_t *x1, int64_t ld_x1, const int8_t *
             return fail(QMM_ERR_NCCL, std::string("NCCL asynchronous error: ") + nccl().GetErrorString(async));
     }
     return QMM_OK;
+}
+
+
+// ---------------------------------------------------------------------------------------------------------
+// npu_mm_reduce_scatter_base and npu_all_gather_base_mm
+// (op_plugin/ops/base_ops/opapi/MatmulReduceScatterBaseKernelNpuOpApi.cpp:22-42,
+//  AllGatherBaseMatmulKernelNpuOpApi.cpp:22-60).
+// ---------------------------------------------------------------------------------------------------------
+namespace qmm {
+namespace {
+
+int find_comm(const char *fn, const char *hcom, Comm *out) {
+    if (hcom == nullptr || hcom[0] == '\0') return fail(QMM_ERR_INVALID_ARGUMENT, std::string(fn) + ": empty communicator name");
+    std::lock_guard<std::mutex> lock(g_comm_mutex);
+    auto it = g_comms.find(hcom);
+    if (it == g_comms.end()) return fail(QMM_ERR_NOT_FOUND, std::string("communicator '") + hcom + "' is not registered");
+    *out = it->second;
+    return QMM_OK;
+}
+
+int check_dense_operands(const char *fn, const void *x1, int dtype, int64_t ld_x1, const void *x2, int64_t sk, int64_t sn,
+                         int64_t M, int64_t N, int64_t K) {
+    const std::string f(fn);
+    QMM_REQUIRE(M >= 0 && N >= 0 && K >= 0, f + ": negative dimension");
+    QMM_REQUIRE(dtype == QMM_DTYPE_BF16 || dtype == QMM_DTYPE_F16, f + ": operands must be bf16 or f16");
+    if (M > 0 && N > 0 && K > 0) {
+        QMM_REQUIRE(x1 != nullptr && x2 != nullptr, f + ": NULL operand");
+        QMM_REQUIRE(ld_x1 >= K, f + ": ld_x1 smaller than K");
+        QMM_REQUIRE(sk == 1 || sn == 1, f + ": x2 must have a unit stride along K or N");
+    }
+    return QMM_OK;
+}
+
+// draws the next epoch and the CTA-counter target of a reduce-scatter (which = 0) or all-gather (1) launch
+int next_sg_epoch(const char *hcom, int which, uint32_t grid, uint32_t *epoch, uint32_t *done_target) {
+    std::lock_guard<std::mutex> lock(g_comm_mutex);
+    auto it = g_comms.find(hcom);
+    if (it == g_comms.end()) return fail(QMM_ERR_NOT_FOUND, std::string("communicator '") + hcom + "' is not registered");
+    *epoch = ++it->second.peer.epoch;
+    uint32_t &calls = which == 0 ? it->second.peer.rs_calls : it->second.peer.ag_calls;
+    *done_target = ++calls * grid;
+    ++it->second.stat_peer;
+    return QMM_OK;
+}
+
+void fill_sg(PeerSgParams &pp, const Comm &c) {
+    for (int r = 0; r < kPeerMaxRanks; ++r) pp.base[r] = c.peer.base[r];
+    pp.world = c.nranks;
+    pp.rank = c.rank;
+    pp.area_off = kPeerFlagBytes;
+    pp.status = device_status_word();
+    pp.status_at_launch = device_status_peek(false);
+}
+
+bool peer_usable(const Comm &c, size_t half_need) {
+    return c.nranks > 1 && c.nranks <= kPeerMaxRanks && !peer_path_disabled() && peer_half_bytes(c.peer.bytes) >= half_need;
+}
+
+}  // namespace
+}  // namespace qmm
+
+extern "C" int qmm_mm_reduce_scatter_workspace_size(int64_t M, int64_t N, int64_t K, int nranks, size_t *bytes) {
+    using namespace qmm;
+    (void)K;
+    QMM_REQUIRE(bytes != nullptr, "qmm_mm_reduce_scatter_workspace_size: bytes is NULL");
+    QMM_REQUIRE(M >= 0 && N >= 0 && nranks >= 1, "qmm_mm_reduce_scatter_workspace_size: bad argument");
+    // NCCL path: the fp32 partial [M, N] and the fp32 reduced rows [M / nranks, N]
+    *bytes = align256(static_cast<size_t>(M) * N * 4) + align256(static_cast<size_t>((M + nranks - 1) / nranks) * N * 4);
+    return QMM_OK;
+}
+
+extern "C" int qmm_mm_reduce_scatter(const void *x1, int dtype, int64_t ld_x1, const void *x2, int64_t x2_stride_k,
+                                     int64_t x2_stride_n, const void *bias, void *out, int64_t ld_out, int64_t M,
+                                     int64_t N, int64_t K, const char *hcom, const char *reduce_op, int64_t comm_turn,
+                                     void *workspace, size_t workspace_bytes, void *stream) {
+    using namespace qmm;
+    const char *fn = "qmm_mm_reduce_scatter";
+    QMM_REQUIRE(reduce_op != nullptr && std::string(reduce_op) == "sum",
+                std::string(fn) + ": reduce_op must be 'sum', got '" + (reduce_op ? reduce_op : "") + "'");
+    QMM_REQUIRE(comm_turn >= 0, std::string(fn) + ": comm_turn must be non-negative");
+    int rc = check_dense_operands(fn, x1, dtype, ld_x1, x2, x2_stride_k, x2_stride_n, M, N, K);
+    if (rc != QMM_OK) return rc;
+    Comm c;
+    rc = find_comm(fn, hcom, &c);
+    if (rc != QMM_OK) return rc;
+    QMM_REQUIRE(M % c.nranks == 0, std::string(fn) + ": M must be divisible by the communicator's size");
+    if (M == 0 || N == 0) return QMM_OK;
+    QMM_REQUIRE(out != nullptr && ld_out >= N, std::string(fn) + ": out is NULL or ld_out smaller than N");
+    int dev = 0;
+    QMM_CUDA_OK(cudaGetDevice(&dev));
+    QMM_REQUIRE(dev == c.device, std::string(fn) + ": communicator belongs to another device");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int64_t rows_per = M / c.nranks;
+
+    DenseParams d;
+    memset(&d, 0, sizeof(d));
+    d.a = x1;
+    d.ld_a = ld_x1;
+    d.b = x2;
+    d.b_sk = x2_stride_k;
+    d.b_sn = x2_stride_n;
+    d.dtype = dtype;
+    d.M = M;
+    d.N = N;
+    d.K = K;
+    if (c.nranks == 1) {  // nothing to exchange: the matmul alone
+        d.mode = kDenseOutCast;
+        d.out = out;
+        d.ld_out = ld_out;
+        d.bias = bias;
+        return launch_dense_gemm(d, s);
+    }
+    if (peer_usable(c, align256(static_cast<size_t>(M) * N * 4))) {
+        cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+        QMM_CUDA_OK(cudaStreamIsCapturing(s, &capture));
+        if (capture != cudaStreamCaptureStatusNone)
+            return fail(QMM_ERR_UNSUPPORTED, std::string(fn) + ": the peer-memory path cannot be captured in a CUDA graph; "
+                                                               "set QMM_ALLREDUCE=nccl on every rank");
+        // matmul whose epilogue stores the fp32 rows into the owners' regions, then the owner's sum
+        d.mode = kDenseOutPush;
+        for (int r = 0; r < kPeerMaxRanks; ++r) d.base[r] = c.peer.base[r];
+        d.area_off = kPeerFlagBytes;
+        d.world = c.nranks;
+        d.rank = c.rank;
+        d.rows_per = rows_per;
+        rc = launch_dense_gemm(d, s);
+        if (rc != QMM_OK) return rc;
+        PeerSgParams pp;
+        fill_sg(pp, c);
+        const uint32_t grid = static_cast<uint32_t>(sm_count());
+        rc = next_sg_epoch(hcom, 0, grid, &pp.epoch, &pp.done_target);
+        if (rc != QMM_OK) return rc;
+        pp.flag_off = kPeerSgFlagOffset;
+        pp.rows = rows_per;
+        pp.cols = N;
+        pp.bias = bias;
+        pp.out = out;
+        pp.ld_out = ld_out;
+        if (dtype == QMM_DTYPE_BF16)
+            peer_reduce_scatter_kernel<__nv_bfloat16><<<grid, kPeerThreads, 0, s>>>(pp);
+        else
+            peer_reduce_scatter_kernel<__half><<<grid, kPeerThreads, 0, s>>>(pp);
+        QMM_CUDA_OK(cudaGetLastError());
+        return QMM_OK;
+    }
+    // NCCL: fp32 partial -> ncclReduceScatter(sum) -> bias and cast
+    rc = nccl_ready();
+    if (rc != QMM_OK) return rc;
+    size_t need = 0;
+    qmm_mm_reduce_scatter_workspace_size(M, N, K, c.nranks, &need);
+    if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+        return fail(QMM_ERR_WORKSPACE, std::string(fn) + ": workspace missing, not 256-byte aligned or smaller than "
+                                                         "qmm_mm_reduce_scatter_workspace_size reports");
+    float *partial = static_cast<float *>(workspace);
+    float *reduced = reinterpret_cast<float *>(static_cast<uint8_t *>(workspace) + align256(static_cast<size_t>(M) * N * 4));
+    d.mode = kDenseOutPush;  // with one "owner" spanning all rows this is a plain fp32 [M, N] output
+    d.base[0] = reinterpret_cast<uint8_t *>(partial);
+    d.area_off = 0;
+    d.world = 1;
+    d.rank = 0;
+    d.rows_per = M;
+    rc = launch_dense_gemm(d, s);
+    if (rc != QMM_OK) return rc;
+    QMM_CUDA_OK(cudaEventRecord(c.chunk_ready[0], s));
+    QMM_CUDA_OK(cudaStreamWaitEvent(c.stream, c.chunk_ready[0], 0));
+    QMM_NCCL_OK(nccl().ReduceScatter(partial, reduced, static_cast<size_t>(rows_per) * N, ncclFloat32, ncclSum, c.comm,
+                                     c.stream));
+    QMM_CUDA_OK(cudaEventRecord(c.done, c.stream));
+    QMM_CUDA_OK(cudaStreamWaitEvent(s, c.done, 0));
+    const int64_t total = rows_per * N;
+    if (dtype == QMM_DTYPE_BF16)
+        cast_rows_kernel<__nv_bfloat16><<<static_cast<unsigned>((total + 255) / 256), 256, 0, s>>>(
+            reduced, static_cast<const __nv_bfloat16 *>(bias), static_cast<__nv_bfloat16 *>(out), ld_out, rows_per, N);
+    else
+        cast_rows_kernel<__half><<<static_cast<unsigned>((total + 255) / 256), 256, 0, s>>>(
+            reduced, static_cast<const __half *>(bias), static_cast<__half *>(out), ld_out, rows_per, N);
+    QMM_CUDA_OK(cudaGetLastError());
+    {
+        std::lock_guard<std::mutex> lock(g_comm_mutex);
+        auto it = g_comms.find(hcom);
+        if (it != g_comms.end()) ++it->second.stat_nccl;
+    }
+    return QMM_OK;
+}
+
+extern "C" int qmm_all_gather_mm_workspace_size(int64_t M, int64_t N, int64_t K, int nranks, size_t *bytes) {
+    using namespace qmm;
+    (void)N;
+    QMM_REQUIRE(bytes != nullptr, "qmm_all_gather_mm_workspace_size: bytes is NULL");
+    QMM_REQUIRE(M >= 0 && K >= 0 && nranks >= 1, "qmm_all_gather_mm_workspace_size: bad argument");
+    *bytes = align256(static_cast<size_t>(M) * nranks * K * 2);  // the gathered x1 when the caller does not want it back
+    return QMM_OK;
+}
+
+extern "C" int qmm_all_gather_mm(const void *x1, int dtype, int64_t ld_x1, const void *x2, int64_t x2_stride_k,
+                                 int64_t x2_stride_n, const void *bias, void *out, int64_t ld_out, void *gather_out,
+                                 int64_t ld_gather, int64_t M, int64_t N, int64_t K, const char *hcom,
+                                 int64_t gather_index, int64_t comm_turn, void *workspace, size_t workspace_bytes,
+                                 void *stream) {
+    using namespace qmm;
+    const char *fn = "qmm_all_gather_mm";
+    QMM_REQUIRE(gather_index == 0, std::string(fn) + ": only gather_index == 0 (gather x1 along its rows) is supported");
+    QMM_REQUIRE(comm_turn >= 0, std::string(fn) + ": comm_turn must be non-negative");
+    int rc = check_dense_operands(fn, x1, dtype, ld_x1, x2, x2_stride_k, x2_stride_n, M, N, K);
+    if (rc != QMM_OK) return rc;
+    Comm c;
+    rc = find_comm(fn, hcom, &c);
+    if (rc != QMM_OK) return rc;
+    if (M == 0) return QMM_OK;
+    QMM_REQUIRE(N == 0 || (out != nullptr && ld_out >= N), std::string(fn) + ": out is NULL or ld_out smaller than N");
+    QMM_REQUIRE(gather_out == nullptr || ld_gather >= K, std::string(fn) + ": ld_gather smaller than K");
+    int dev = 0;
+    QMM_CUDA_OK(cudaGetDevice(&dev));
+    QMM_REQUIRE(dev == c.device, std::string(fn) + ": communicator belongs to another device");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int W = c.nranks;
+
+    // where the gathered [W * M, K] matrix lives: the caller's tensor, or the workspace
+    uint8_t *gathered = static_cast<uint8_t *>(gather_out);
+    int64_t ld_g = ld_gather;
+    if (gathered == nullptr && W > 1 && K > 0) {
+        size_t need = 0;
+        qmm_all_gather_mm_workspace_size(M, N, K, W, &need);
+        if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+            return fail(QMM_ERR_WORKSPACE, std::string(fn) + ": workspace missing, not 256-byte aligned or smaller than "
+                                                             "qmm_all_gather_mm_workspace_size reports");
+        gathered = static_cast<uint8_t *>(workspace);
+        ld_g = K;
+    }
+    const size_t shard_bytes = static_cast<size_t>(M) * K * 2;
+    if (gathered != nullptr && K > 0) {
+        // own shard into its slot of the gathered matrix
+        QMM_CUDA_OK(cudaMemcpy2DAsync(gathered + static_cast<size_t>(c.rank) * M * ld_g * 2, static_cast<size_t>(ld_g) * 2, x1,
+                                      static_cast<size_t>(ld_x1) * 2, static_cast<size_t>(K) * 2, static_cast<size_t>(M),
+                                      cudaMemcpyDeviceToDevice, s));
+    }
+    if (W > 1 && K > 0) {
+        if (peer_usable(c, align256(shard_bytes))) {
+            cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+            QMM_CUDA_OK(cudaStreamIsCapturing(s, &capture));
+            if (capture != cudaStreamCaptureStatusNone)
+                return fail(QMM_ERR_UNSUPPORTED, std::string(fn) + ": the peer-memory path cannot be captured in a CUDA "
+                                                                   "graph; set QMM_ALLREDUCE=nccl on every rank");
+            // own shard, densely packed, into this rank's region for the peers to pull
+            QMM_CUDA_OK(cudaMemcpy2DAsync(c.peer.base[c.rank] + kPeerFlagBytes, static_cast<size_t>(K) * 2, x1,
+                                          static_cast<size_t>(ld_x1) * 2, static_cast<size_t>(K) * 2,
+                                          static_cast<size_t>(M), cudaMemcpyDeviceToDevice, s));
+            PeerSgParams pp;
+            fill_sg(pp, c);
+            const uint32_t grid = static_cast<uint32_t>(sm_count());
+            rc = next_sg_epoch(hcom, 1, grid, &pp.epoch, &pp.done_target);
+            if (rc != QMM_OK) return rc;
+            pp.flag_off = kPeerAgFlagOffset;
+            pp.rows = M;
+            pp.cols = K;
+            pp.bias = nullptr;
+            pp.out = gathered;
+            pp.ld_out = ld_g;
+            peer_all_gather_kernel<<<grid, kPeerThreads, 0, s>>>(pp);
+            QMM_CUDA_OK(cudaGetLastError());
+        } else {
+            rc = nccl_ready();
+            if (rc != QMM_OK) return rc;
+            QMM_REQUIRE(ld_g == K && ld_x1 == K, std::string(fn) + ": the NCCL path needs contiguous x1 and gather output");
+            QMM_CUDA_OK(cudaEventRecord(c.chunk_ready[0], s));
+            QMM_CUDA_OK(cudaStreamWaitEvent(c.stream, c.chunk_ready[0], 0));
+            QMM_NCCL_OK(nccl().AllGather(x1, gathered, static_cast<size_t>(M) * K,
+                                         dtype == QMM_DTYPE_BF16 ? ncclBfloat16 : ncclFloat16, c.comm, c.stream));
+            QMM_CUDA_OK(cudaEventRecord(c.done, c.stream));
+            QMM_CUDA_OK(cudaStreamWaitEvent(s, c.done, 0));
+            std::lock_guard<std::mutex> lock(g_comm_mutex);
+            auto it = g_comms.find(hcom);
+            if (it != g_comms.end()) ++it->second.stat_nccl;
+        }
+    }
+    if (N == 0) return QMM_OK;
+    DenseParams d;
+    memset(&d, 0, sizeof(d));
+    d.a = (W > 1 && K > 0) ? static_cast<const void *>(gathered) : x1;
+    d.ld_a = (W > 1 && K > 0) ? ld_g : ld_x1;
+    d.b = x2;
+    d.b_sk = x2_stride_k;
+    d.b_sn = x2_stride_n;
+    d.dtype = dtype;
+    d.M = M * W;
+    d.N = N;
+    d.K = K;
+    d.mode = kDenseOutCast;
+    d.out = out;
+    d.ld_out = ld_out;
+    d.bias = bias;
+    return launch_dense_gemm(d, s);
 }

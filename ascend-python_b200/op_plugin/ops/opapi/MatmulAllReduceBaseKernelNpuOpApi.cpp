@@ -94,14 +94,19 @@ at::Tensor npu_mm_all_reduce_base(const at::Tensor &x1, const at::Tensor &x2, c1
     size_t workspace_size = 0;
     EXEC_QMM_CMD(qmm_quant_matmul_workspace_size, M, N, K, QMM_ALGO_AUTO, &workspace_size);
     at::Tensor workspace = op_plugin_utils::qmm_workspace(a, workspace_size);
-    EXEC_QMM_CMD(qmm_mm_all_reduce, static_cast<const int8_t *>(a.const_data_ptr()), std::max<int64_t>(K, 1),
-                 static_cast<const int8_t *>(b.const_data_ptr()), stride_k, stride_n,
-                 static_cast<const float *>(scale_c.const_data_ptr()), scale_c.numel(),
-                 static_cast<const float *>(op_plugin_utils::opt_ptr(pertoken_c)), op_plugin_utils::opt_ptr(bias_c),
-                 bias_c.defined() ? op_plugin_utils::qmm_dtype(bias_c.scalar_type()) : QMM_DTYPE_NONE,
-                 result.data_ptr(), op_plugin_utils::qmm_dtype(out_type), N, M, N, K, hcom_str.c_str(),
-                 reduce_op_str.c_str(), comm_turn, workspace.defined() ? workspace.data_ptr() : nullptr,
-                 workspace_size, op_plugin_utils::current_stream(a));
+    const int ret = qmm_mm_all_reduce(
+        static_cast<const int8_t *>(a.const_data_ptr()), std::max<int64_t>(K, 1),
+        static_cast<const int8_t *>(b.const_data_ptr()), stride_k, stride_n,
+        static_cast<const float *>(scale_c.const_data_ptr()), scale_c.numel(),
+        static_cast<const float *>(op_plugin_utils::opt_ptr(pertoken_c)), op_plugin_utils::opt_ptr(bias_c),
+        bias_c.defined() ? op_plugin_utils::qmm_dtype(bias_c.scalar_type()) : QMM_DTYPE_NONE, result.data_ptr(),
+        op_plugin_utils::qmm_dtype(out_type), N, M, N, K, hcom_str.c_str(), reduce_op_str.c_str(), comm_turn,
+        workspace.defined() ? workspace.data_ptr() : nullptr, workspace_size, op_plugin_utils::current_stream(a));
+    if (ret == QMM_ERR_DEVICE_TIMEOUT) {
+        // an earlier kernel was cut short: its scratch may hold partial sums, hand out fresh buffers from now on
+        op_plugin_utils::qmm_workspace_reset();
+    }
+    TORCH_CHECK(ret == 0, "call qmm_mm_all_reduce failed, detail:", qmm_last_error());
     return result;
 }
 

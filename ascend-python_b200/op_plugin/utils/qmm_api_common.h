@@ -38,6 +38,21 @@ void *current_stream(const at::Tensor &like);
 // `family` separates kernel families: each relies on the state it left in its own buffer.
 at::Tensor qmm_workspace(const at::Tensor &like, size_t bytes, int family = 0);
 
+// Drops every cached scratch buffer: the next request gets a fresh zero-filled one.  For the case that a kernel
+// was cut short (a bounded device-side wait gave up) and left its scratch in an unknown state.
+void qmm_workspace_reset();
+
+// The second matmul operand as the C ABI addresses it, x2[k * stride_k + n * stride_n] with one unit stride:
+// a row-major [K, N] tensor and the transposed view of a row-major [N, K] tensor are taken as stored
+// (cf. the transpose-aware matmul of the reference, op_plugin/ops/base_ops/aclops/MmKernelNpu.cpp:40-53),
+// anything else is made contiguous first.
+struct MatmulOperandB {
+    at::Tensor tensor;
+    int64_t stride_k;
+    int64_t stride_n;
+};
+MatmulOperandB describe_operand_b(const at::Tensor &x2, int64_t K, int64_t N);
+
 // data pointer of an optional tensor (nullptr when absent)
 inline const void *opt_ptr(const at::Tensor &t) { return t.defined() ? t.const_data_ptr() : nullptr; }
 

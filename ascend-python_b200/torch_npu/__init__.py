@@ -73,6 +73,21 @@ def npu_mm_all_reduce_base(x1, x2, hcom, *, reduce_op="sum", bias=None, antiquan
                                        comm_turn=comm_turn)
 
 
+def npu_mm_reduce_scatter_base(self, x2, hcom, world_size, *, reduce_op="sum", bias=None, comm_turn=0):
+    if self.is_cuda and world_size > 1:
+        # first half of a region: the fp32 rows of all ranks that this rank will add up
+        _ensure_peer_bytes(hcom, self.shape[0] * x2.shape[-1] * 4, self.device)
+    return _ops.npu_mm_reduce_scatter_base(self, x2, hcom, world_size, reduce_op=reduce_op, bias=bias,
+                                           comm_turn=comm_turn)
+
+
+def npu_all_gather_base_mm(self, x2, hcom, world_size, *, bias=None, gather_index=0, gather_output=True, comm_turn=0):
+    if self.is_cuda and world_size > 1:
+        _ensure_peer_bytes(hcom, self.numel() * self.element_size(), self.device)  # this rank's shard of x1
+    return _ops.npu_all_gather_base_mm(self, x2, hcom, world_size, bias=bias, gather_index=gather_index,
+                                       gather_output=gather_output, comm_turn=comm_turn)
+
+
 _comm_names = {}
 
 
@@ -115,13 +130,29 @@ def get_comm_name(group=None) -> str:
 _peer_memory = {}  # communicator name -> dict(bytes, tensor, handle) or None when unavailable
 
 
+def _ensure_peer_bytes(name: str, half_bytes: int, device) -> None:
+    """Peer-mapped regions whose two halves hold at least ``half_bytes`` each (see _ensure_peer_memory)."""
+    _ensure_peer_region(name, 65536 + 2 * ((int(half_bytes) + 255) // 256 * 256), device)
+
+
 def _ensure_peer_memory(name: str, M: int, N: int, device) -> None:
-    """Gives the communicator ``name`` peer-mapped regions large enough for an allreduce of [M, N].
+    """Gives the communicator ``name`` peer-mapped regions large enough for an allreduce of [M, N]."""
+    info = _comm_names.get(name)
+    if not isinstance(info, dict):
+        return
+    need = ctypes.c_size_t(0)
+    _capi.check(_capi.lib().qmm_comm_peer_memory_size(M, N, info["world"], ctypes.byref(need)),
+                "qmm_comm_peer_memory_size")
+    _ensure_peer_region(name, int(need.value), device)
+
+
+def _ensure_peer_region(name: str, need_bytes: int, device) -> None:
+    """Gives the communicator ``name`` peer-mapped regions of at least ``need_bytes``.
 
     The regions come from torch's symmetric memory (one allocation per rank, mapped by all ranks of
     the node); the library then reduces and gathers through NVLink loads instead of NCCL.  The first
     call, and any call that needs a larger region, is collective: all ranks reach it with the same
-    M and N.  Where symmetric memory is not available the communicator stays on NCCL.
+    size.  Where symmetric memory is not available the communicator stays on NCCL.
     QMM_ALLREDUCE = nccl | p2p | multimem forces a path; unset, peer memory with plain peer loads is used
     (measured on B200, M=4096, N=8192: 381 us against 424 us with NCCL on two GPUs, 250 us against 356 us on
     eight; in-switch reduction measured the same as plain loads, which keep the rank-order sum).
@@ -136,17 +167,15 @@ def _ensure_peer_memory(name: str, M: int, N: int, device) -> None:
     if world < 2 or world > 8:
         return
     lib = _capi.lib()
-    need = ctypes.c_size_t(0)
-    _capi.check(lib.qmm_comm_peer_memory_size(M, N, world, ctypes.byref(need)), "qmm_comm_peer_memory_size")
     cur = _peer_memory.get(name, {})
-    if cur is None or (cur and cur["bytes"] >= need.value):
+    if cur is None or (cur and cur["bytes"] >= need_bytes):
         return
     try:
         import torch
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm
 
-        nbytes = max(int(need.value), 32 << 20)
+        nbytes = max(int(need_bytes), 32 << 20)
         nbytes = (nbytes + (2 << 20) - 1) // (2 << 20) * (2 << 20)
         if cur:
             _capi.check(lib.qmm_comm_attach_peer_memory(name.encode(), None, None, 0), "qmm_comm_attach_peer_memory")

@@ -292,6 +292,42 @@ QMM_API int qmm_mm_all_reduce(const int8_t *x1, int64_t ld_x1, const int8_t *x2,
                               const char *hcom, const char *reduce_op, int64_t comm_turn, void *workspace,
                               size_t workspace_bytes, void *stream);
 
+/*
+ * Matmul + reduce-scatter (torch op `npu_mm_reduce_scatter_base`,
+ * op_plugin/ops/base_ops/opapi/MatmulReduceScatterBaseKernelNpuOpApi.cpp:22-42; golden formula
+ * test/test_custom_ops/test_mm_reduce_scatter_base.py:69-81):
+ *   out = rows [rank * M/W, (rank+1) * M/W) of cast( sum_r float(x1_r) @ float(x2_r) + bias )
+ * x1: [M, K] bf16/f16 (dtype), row pitch ld_x1; x2: [K, N] of dtype addressed as in qmm_quant_matmul (row-major or
+ * the transposed view of a row-major [N, K]); bias: [N] of dtype or NULL; out: [M/W, N] of dtype.  M must be
+ * divisible by the communicator's size W.  Every rank's products are accumulated in fp32 and added in fp32 in rank
+ * order before the single rounding.  With peer memory attached (qmm_comm_attach_peer_memory; the first half of a
+ * region must hold M*N*4 bytes) the matmul's epilogue stores its fp32 rows straight into the owning rank's region
+ * and one kernel per rank adds them; otherwise the fp32 partial goes through ncclReduceScatter and needs the
+ * workspace (256-byte aligned).  comm_turn is accepted for signature compatibility.
+ */
+QMM_API int qmm_mm_reduce_scatter_workspace_size(int64_t M, int64_t N, int64_t K, int nranks, size_t *bytes);
+QMM_API int qmm_mm_reduce_scatter(const void *x1, int dtype, int64_t ld_x1, const void *x2, int64_t x2_stride_k,
+                                  int64_t x2_stride_n, const void *bias, void *out, int64_t ld_out, int64_t M,
+                                  int64_t N, int64_t K, const char *hcom, const char *reduce_op, int64_t comm_turn,
+                                  void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * All-gather + matmul (torch op `npu_all_gather_base_mm`,
+ * op_plugin/ops/base_ops/opapi/AllGatherBaseMatmulKernelNpuOpApi.cpp:22-60; golden formula
+ * test/test_custom_ops/test_all_gather_base_mm.py:72-78):
+ *   gathered = concat_r x1_r  ([W * M, K]);   out = cast( float(gathered) @ float(x2) + bias )   ([W * M, N])
+ * M is this rank's row count.  gather_out ([W * M, K], row pitch ld_gather) receives the gathered matrix, or is
+ * NULL, in which case the workspace holds it.  Only gather_index == 0 is supported.  With peer memory attached
+ * (first half >= M*K*2 bytes) the shards are pulled over NVLink by the library's own kernel, otherwise by
+ * ncclAllGather (contiguous x1 and gather_out required).
+ */
+QMM_API int qmm_all_gather_mm_workspace_size(int64_t M, int64_t N, int64_t K, int nranks, size_t *bytes);
+QMM_API int qmm_all_gather_mm(const void *x1, int dtype, int64_t ld_x1, const void *x2, int64_t x2_stride_k,
+                              int64_t x2_stride_n, const void *bias, void *out, int64_t ld_out, void *gather_out,
+                              int64_t ld_gather, int64_t M, int64_t N, int64_t K, const char *hcom,
+                              int64_t gather_index, int64_t comm_turn, void *workspace, size_t workspace_bytes,
+                              void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -18,6 +18,12 @@ file follows:
 * ``test/test_custom_ops/test_npu_rms_norm.py:10-34`` — numpy golden
   (``supported_op_exec``) compared with the device op (``custom_op_exec``).
 
+Three operators that DO exist in the reference are restated here too and ARE
+pinned against outputs of the reference's own golden functions, executed from
+the reference's test files (tests/golden/make_rms_norm_golden.py,
+tests/golden/make_mc2_golden.py): ``rms_norm``, ``mm_reduce_scatter``,
+``all_gather_mm``.
+
 Every choice the reference leaves open is fixed here, once:
 
 * dynamic quant: ``scale = amax / 127`` and ``q = rint(x / scale)`` with true
@@ -254,6 +260,47 @@ def mm_all_reduce(x1_list, x2_list, scale, pertoken_list, *, bias=None, output_d
                             output_dtype=output_dtype).to(torch.float32).numpy()
         total = part if total is None else (total + part).astype(np.float32)
     return total, _round_to(total, output_dtype)
+
+
+# ---------------------------------------------------------------------------
+# npu_mm_reduce_scatter_base / npu_all_gather_base_mm (present in the reference, with tests)
+# ---------------------------------------------------------------------------
+
+
+def mm_reduce_scatter(x1_list, x2_list, world_size, *, bias=None):
+    """Per-rank expected outputs of npu_mm_reduce_scatter_base.
+
+    Restates ``_construct_excepted_result`` of test/test_custom_ops/test_mm_reduce_scatter_base.py:69-81:
+    fp32 matmul per rank, partial results added in rank order in fp32, one cast to the input dtype, rows
+    sliced by rank.  (``bias`` - not exercised by the reference test - is added to the fp32 sum once.)
+    Pinned: tests/golden/mc2_reference.npz holds outputs of the reference's own function.
+    """
+    out = None
+    for i in range(world_size):
+        out_single = torch.matmul(x1_list[i].to(torch.float), x2_list[i].to(torch.float))
+        out = out_single if out is None else torch.add(out, out_single)
+    if bias is not None:
+        out = out + bias.to(torch.float)[None, :]
+    out = out.to(x1_list[0].dtype)
+    index = x1_list[0].shape[0] // world_size
+    return [out[index * i:index * (i + 1), :] for i in range(world_size)]
+
+
+def all_gather_mm(x1_list, x2_list, world_size, *, bias=None):
+    """(per-rank expected matmul outputs, gathered x1) of npu_all_gather_base_mm.
+
+    Restates ``_construct_excepted_result`` of test/test_custom_ops/test_all_gather_base_mm.py:72-78:
+    x1 of all ranks concatenated along the rows, fp32 matmul with the rank's own x2, one cast.
+    Pinned by tests/golden/mc2_reference.npz like mm_reduce_scatter.
+    """
+    gather_out = torch.cat(x1_list)
+    out_list = []
+    for i in range(world_size):
+        y = torch.matmul(gather_out.to(torch.float), x2_list[i].to(torch.float))
+        if bias is not None:
+            y = y + bias.to(torch.float)[None, :]
+        out_list.append(y.to(gather_out.dtype))
+    return out_list, gather_out
 
 
 # ---------------------------------------------------------------------------

@@ -76,7 +76,13 @@ def test_ops_registered_with_reference_signatures(pkg):
     assert "str hcom" in str(ops.npu_mm_all_reduce_base.default._schema)
     assert 'str reduce_op="sum"' in str(ops.npu_mm_all_reduce_base.default._schema)
     assert "int antiquant_group_size=0" in str(ops.npu_weight_quant_batchmatmul.default._schema)
-    # the reference's own entry, verbatim (op_plugin/config/v2r1/op_plugin_functions.yaml:2113)
+    # the reference's own entries, verbatim (op_plugin/config/v2r1/op_plugin_functions.yaml:2310-2313, :2113)
+    assert str(ops.npu_mm_reduce_scatter_base.default._schema) == (
+        'npu::npu_mm_reduce_scatter_base(Tensor self, Tensor x2, str hcom, int world_size, *, str reduce_op="sum", '
+        "Tensor? bias=None, int comm_turn=0) -> Tensor")
+    assert str(ops.npu_all_gather_base_mm.default._schema) == (
+        "npu::npu_all_gather_base_mm(Tensor self, Tensor x2, str hcom, int world_size, *, Tensor? bias=None, "
+        "int gather_index=0, bool gather_output=True, int comm_turn=0) -> (Tensor, Tensor)")
     assert str(ops.npu_rms_norm.default._schema) == \
         "npu::npu_rms_norm(Tensor self, Tensor gamma, float epsilon=9.9999999999999995e-07) -> (Tensor, Tensor)"
     # CUDA is the only backend: a CPU tensor has nowhere to go
@@ -91,6 +97,7 @@ def test_torch_npu_shim_names(pkg):
     finally:
         sys.path.pop(0)
     for name in ("npu_dynamic_quant", "npu_quant_matmul", "npu_weight_quant_batchmatmul", "npu_mm_all_reduce_base",
+                 "npu_mm_reduce_scatter_base", "npu_all_gather_base_mm", "npu_rms_norm", "npu_rms_norm_dynamic_quant",
                  "get_comm_name"):
         assert callable(getattr(torch_npu, name))
     assert torch_npu.comm_name_for("tp", 8) == "qmm_comm_tp_8"
@@ -116,8 +123,9 @@ def test_codegen_declarations(tmp_path):
     with pytest.raises(ValueError):
         gen.parse_schema("f(Dimname d) -> Tensor", "op_api")
     ops = gen.run(PKG_DIR / "op_plugin" / "config" / "op_plugin_functions.yaml", tmp_path)
-    assert [o.name for o in ops][:6] == ["npu_dynamic_quant", "npu_quant_matmul", "npu_weight_quant_batchmatmul",
-                                         "npu_mm_all_reduce_base", "npu_rms_norm", "npu_rms_norm_dynamic_quant"]
+    assert [o.name for o in ops] == ["npu_dynamic_quant", "npu_quant_matmul", "npu_weight_quant_batchmatmul",
+                                     "npu_mm_all_reduce_base", "npu_rms_norm", "npu_rms_norm_dynamic_quant",
+                                     "npu_mm_reduce_scatter_base", "npu_all_gather_base_mm"]
     lib_cpp = (tmp_path / "TorchLibrary.cpp").read_text()
     assert "TORCH_LIBRARY_FRAGMENT(npu, m)" in lib_cpp and "TORCH_LIBRARY_IMPL(npu, CUDA, m)" in lib_cpp
     assert "return op_api::npu_quant_matmul(x1, x2, scale, offset, pertoken_scale, bias, output_dtype);" in \

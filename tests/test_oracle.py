@@ -249,3 +249,27 @@ def test_dynamic_quant_non_finite_rows():
     q, s = O.dynamic_quant(x)
     assert torch.isinf(s[0]) and torch.isnan(s[1]) and s[2].item() == np.float32(4.0) / np.float32(127.0)
     assert q[0].tolist() == [0, 0, 0, 0] and q[1].tolist() == [0, 0, 0, 0] and q[2].tolist() == [32, 64, -127, 0]
+
+
+def test_mc2_oracles_pinned_to_reference_golden():
+    """oracle.mm_reduce_scatter / all_gather_mm against outputs of the reference's own golden functions
+    (executed from its test files by tests/golden/make_mc2_golden.py): bit for bit, 2, 4 and 8 ranks."""
+    import importlib.util
+
+    from oracle import qmm_oracle as O
+
+    spec = importlib.util.spec_from_file_location("make_mc2_golden", GOLDEN / "make_mc2_golden.py")
+    mk = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mk)
+    g = np.load(GOLDEN / "mc2_reference.npz")
+    for world in (2, 4, 8):
+        rs_x1, rs_x2, ag_x1, ag_x2 = mk.mc2_inputs(world)
+        rs = O.mm_reduce_scatter(rs_x1, rs_x2, world)
+        ag, gathered = O.all_gather_mm(ag_x1, ag_x2, world)
+        assert mk.digest(rs) == str(g[f"rs{world}_sha256"]) and mk.digest(ag) == str(g[f"ag{world}_sha256"])
+        assert rs[0].shape == (128 // world, 256) and ag[0].shape == (16 * world, 256)
+        assert torch.equal(gathered, torch.cat(ag_x1))
+        if world < 8:
+            for r in range(world):
+                assert np.array_equal(rs[r].contiguous().view(torch.int16).numpy(), g[f"rs{world}_out"][r])
+                assert np.array_equal(ag[r].contiguous().view(torch.int16).numpy(), g[f"ag{world}_out"][r])
