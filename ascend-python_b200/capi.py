@@ -33,7 +33,7 @@ EXPORTED_SYMBOLS = (
     "qmm_weight_quant_batchmatmul_prepacked_workspace_size", "qmm_weight_quant_batchmatmul_prepacked",
     "qmm_rms_norm", "qmm_rms_norm_dynamic_quant", "qmm_comm_stats", "qmm_int8_mma_peak", "qmm_noalloc_status",
     "qmm_mm_reduce_scatter_workspace_size", "qmm_mm_reduce_scatter", "qmm_all_gather_mm_workspace_size",
-    "qmm_all_gather_mm",
+    "qmm_all_gather_mm", "qmm_quant_matmul_int8_workspace_size", "qmm_quant_matmul_int8",
 )
 NOALLOC_SCRATCH_BYTES = 16 << 20
 
@@ -130,6 +130,13 @@ def lib() -> ctypes.CDLL:
         for name in ("qmm_mm_reduce_scatter_workspace_size", "qmm_mm_reduce_scatter",
                      "qmm_all_gather_mm_workspace_size", "qmm_all_gather_mm"):
             getattr(L, name).restype = c.c_int
+        L.qmm_quant_matmul_int8_workspace_size.argtypes = [c.c_int64, c.c_int64, c.c_int64, c.POINTER(c.c_size_t)]
+        L.qmm_quant_matmul_int8_workspace_size.restype = c.c_int
+        L.qmm_quant_matmul_int8.argtypes = [c.c_void_p, c.c_int64, c.c_void_p, c.c_int64, c.c_int64, c.c_void_p,
+                                            c.c_int64, c.c_void_p, c.c_int64, c.c_void_p, c.c_void_p, c.c_void_p,
+                                            c.c_int64, c.c_int64, c.c_int64, c.c_int64, c.c_void_p, c.c_size_t,
+                                            c.c_void_p]
+        L.qmm_quant_matmul_int8.restype = c.c_int
         L.qmm_comm_unique_id.argtypes = [c.c_void_p]
         L.qmm_comm_init_rank.argtypes = [c.c_char_p, c.c_void_p, c.c_int, c.c_int]
         L.qmm_comm_register.argtypes = [c.c_char_p, c.c_void_p, c.c_int, c.c_int]
@@ -368,3 +375,23 @@ def int8_mma_peak(batches: int = 1024) -> dict:
     a, b, c = ctypes.c_double(0), ctypes.c_double(0), ctypes.c_double(0)
     check(lib().qmm_int8_mma_peak(batches, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c)), "qmm_int8_mma_peak")
     return {"ops_per_clk_per_sm": a.value, "tops": b.value, "sm_mhz": c.value}
+
+
+def quant_matmul_int8(x1, x2, scale, offset=None, pertoken_scale=None, bias=None):
+    """x1 int8 [M,K], x2 int8 [K,N] -> int8 [M,N] requantized (see qmm_quant_matmul_int8)."""
+    assert x1.is_cuda and x1.dtype == torch.int8 and x2.dtype == torch.int8
+    M, K = x1.shape
+    N = x2.shape[1]
+    x1 = x1.contiguous()
+    if x2.stride(0) != 1 and x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    out = torch.empty((M, N), dtype=torch.int8, device=x1.device)
+    n = ctypes.c_size_t(0)
+    check(lib().qmm_quant_matmul_int8_workspace_size(M, N, K, ctypes.byref(n)), "qmm_quant_matmul_int8_workspace_size")
+    ws = get_workspace(x1.device, int(n.value), kind="w8a8_int8")
+    with torch.cuda.device(x1.device):
+        check(lib().qmm_quant_matmul_int8(_ptr(x1), max(K, 1), _ptr(x2), x2.stride(0), x2.stride(1), _ptr(scale),
+                                          scale.numel(), _ptr(offset), 0 if offset is None else offset.numel(),
+                                          _ptr(pertoken_scale), _ptr(bias), _ptr(out), max(N, 1), M, N, K, _ptr(ws),
+                                          int(n.value), _stream()), "qmm_quant_matmul_int8")
+    return out

@@ -1,0 +1,121 @@
+// int8 output of npu_quant_matmul (`output_dtype = int8`, with the optional `offset`).
+//
+// The operator and its arithmetic are not in the reference snapshot; the form below is this build's
+// stated choice (the argument list is the one the task gives: x1, x2, scale, offset, pertoken_scale,
+// bias, output_dtype):
+//     acc[m,n] = sum_k x1[m,k] * x2[k,n] + bias[n]                      int32, exact (bias int32)
+//     v        = float(acc) * scale[n] (* pertoken_scale[m]) (+ offset[n])   fp32, one rounding per operation
+//     out      = clamp(rint(v), -128, 127)                              round half to even
+// It runs as two launches: the W8A8 kernels produce the exact int32 accumulator (their int32 output
+// mode) into scratch, and requant_kernel below makes one pass over it.  That costs 5 bytes of HBM
+// traffic per output element more than an epilogue fused into every matmul kernel would; no
+// configuration of the benchmark uses an int8 output.
+#include "qmm_common.cuh"
+
+extern "C" int qmm_quant_matmul(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_stride_k,
+                                int64_t x2_stride_n, const float *scale, int64_t scale_len,
+                                const float *pertoken_scale, const void *bias, int bias_dtype, void *out,
+                                int out_dtype, int64_t ld_out, int64_t M, int64_t N, int64_t K, int algo,
+                                void *workspace, size_t workspace_bytes, void *stream);
+extern "C" int qmm_quant_matmul_workspace_size(int64_t M, int64_t N, int64_t K, int algo, size_t *bytes);
+
+namespace qmm {
+namespace {
+
+__device__ __forceinline__ int requant_one(int32_t acc, float sc, float pt, bool has_pt, float off, bool has_off) {
+    float v = __fmul_rn(static_cast<float>(acc), sc);
+    if (has_pt) v = __fmul_rn(v, pt);
+    if (has_off) v = __fadd_rn(v, off);
+    return max(-128, min(127, __float2int_rn(v)));
+}
+
+// four columns per thread where N allows
+__global__ void __launch_bounds__(256)
+requant_kernel(const int32_t *__restrict__ acc, int64_t M, int64_t N, const float *__restrict__ scale, int scale_scalar,
+               const float *__restrict__ pertoken, const float *__restrict__ offset, int offset_scalar,
+               int8_t *__restrict__ out, int64_t ld_out) {
+    const bool vec = (N & 3) == 0 && (ld_out & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 3) == 0;
+    const bool has_pt = pertoken != nullptr, has_off = offset != nullptr;
+    if (vec) {
+        const int64_t per_row = N >> 2;
+        const int64_t total = M * per_row;
+        for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+             i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+            const int64_t m = i / per_row, n = (i - m * per_row) << 2;
+            const int4 a = __ldcs(reinterpret_cast<const int4 *>(acc + m * N + n));
+            const float pt = has_pt ? __ldg(pertoken + m) : 1.0f;
+            const int32_t av[4] = {a.x, a.y, a.z, a.w};
+            uint32_t packed = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float sc = scale_scalar ? __ldg(scale) : __ldg(scale + n + j);
+                const float off = has_off ? (offset_scalar ? __ldg(offset) : __ldg(offset + n + j)) : 0.0f;
+                packed |= (static_cast<uint32_t>(requant_one(av[j], sc, pt, has_pt, off, has_off)) & 0xffu) << (8 * j);
+            }
+            *reinterpret_cast<uint32_t *>(out + m * ld_out + n) = packed;
+        }
+    } else {
+        const int64_t total = M * N;
+        for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+             i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+            const int64_t m = i / N, n = i - m * N;
+            const float sc = scale_scalar ? __ldg(scale) : __ldg(scale + n);
+            const float off = has_off ? (offset_scalar ? __ldg(offset) : __ldg(offset + n)) : 0.0f;
+            out[m * ld_out + n] = static_cast<int8_t>(requant_one(acc[i], sc, has_pt ? __ldg(pertoken + m) : 1.0f, has_pt, off, has_off));
+        }
+    }
+}
+
+size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+}  // namespace
+}  // namespace qmm
+
+extern "C" int qmm_quant_matmul_int8_workspace_size(int64_t M, int64_t N, int64_t K, size_t *bytes) {
+    using namespace qmm;
+    QMM_REQUIRE(bytes != nullptr, "qmm_quant_matmul_int8_workspace_size: bytes is NULL");
+    QMM_REQUIRE(M >= 0 && N >= 0 && K >= 0, "qmm_quant_matmul_int8_workspace_size: negative dimension");
+    size_t inner = 0;
+    int rc = qmm_quant_matmul_workspace_size(M, N, K, QMM_ALGO_AUTO, &inner);
+    if (rc != QMM_OK) return rc;
+    // [the matmul's own scratch (zero before first use)][int32 accumulator M x N]
+    *bytes = align256(inner) + align256(static_cast<size_t>(M) * N * 4);
+    return QMM_OK;
+}
+
+extern "C" int qmm_quant_matmul_int8(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_stride_k,
+                                     int64_t x2_stride_n, const float *scale, int64_t scale_len, const float *offset,
+                                     int64_t offset_len, const float *pertoken_scale, const int32_t *bias, int8_t *out,
+                                     int64_t ld_out, int64_t M, int64_t N, int64_t K, void *workspace,
+                                     size_t workspace_bytes, void *stream) {
+    using namespace qmm;
+    QMM_REQUIRE(M >= 0 && N >= 0 && K >= 0, "qmm_quant_matmul_int8: negative dimension");
+    if (M == 0 || N == 0) return QMM_OK;
+    QMM_REQUIRE(out != nullptr && ld_out >= N, "qmm_quant_matmul_int8: out is NULL or ld_out smaller than N");
+    QMM_REQUIRE(scale != nullptr && (scale_len == N || scale_len == 1), "qmm_quant_matmul_int8: scale must have N elements or one");
+    QMM_REQUIRE(offset == nullptr || offset_len == N || offset_len == 1,
+                "qmm_quant_matmul_int8: offset must have N elements or one");
+    size_t need = 0, inner = 0;
+    qmm_quant_matmul_int8_workspace_size(M, N, K, &need);
+    qmm_quant_matmul_workspace_size(M, N, K, QMM_ALGO_AUTO, &inner);
+    if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+        return fail(QMM_ERR_WORKSPACE, "qmm_quant_matmul_int8: workspace missing, not 256-byte aligned or smaller than "
+                                       "qmm_quant_matmul_int8_workspace_size reports");
+    int32_t *acc = reinterpret_cast<int32_t *>(static_cast<uint8_t *>(workspace) + align256(inner));
+    // the matmul kernels want their scratch zeroed; where it sits depends on the shape, and a call of another
+    // shape may have left accumulators there, so it is cleared per call (decode shapes only: inner is 0 for M > 128)
+    if (inner > 0) QMM_CUDA_OK(cudaMemsetAsync(workspace, 0, inner, static_cast<cudaStream_t>(stream)));
+    int rc = qmm_quant_matmul(x1, ld_x1, x2, x2_stride_k, x2_stride_n, nullptr, 0, nullptr, bias,
+                              bias ? QMM_DTYPE_I32 : QMM_DTYPE_NONE, acc, QMM_DTYPE_I32, N, M, N, K, QMM_ALGO_AUTO,
+                              inner ? workspace : nullptr, inner, stream);
+    if (rc != QMM_OK) return rc;
+    const int64_t items = ((N & 3) == 0) ? M * (N >> 2) : M * N;
+    int64_t grid = (items + 255) / 256;
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+    if (grid > cap) grid = cap;
+    requant_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        acc, M, N, scale, (scale_len == 1 && N != 1) ? 1 : 0, pertoken_scale, offset, (offset_len == 1 && N != 1) ? 1 : 0,
+        out, ld_out);
+    QMM_CUDA_OK(cudaGetLastError());
+    return QMM_OK;
+}

@@ -23,15 +23,13 @@ at::Tensor npu_quant_matmul(const at::Tensor &x1, const at::Tensor &x2, const at
     TORCH_CHECK(x1.size(-1) == x2.size(0),
                 "The K-axis in the two inputs of Matmul must be equal, but in reality, the K-axis of x1 is ",
                 x1.size(-1), " and the K-axis of x2 is ", x2.size(0));
-    TORCH_CHECK(!offset.has_value() || !offset->defined(),
-                "npu_quant_matmul: offset only applies to an int8 output, which this build does not produce; "
-                "pass None");
-    TORCH_CHECK(output_dtype.has_value(),
-                "npu_quant_matmul: output_dtype=None selects an int8 output, which this build does not produce; "
-                "pass torch.bfloat16, torch.float16 or torch.int32");
-    const at::ScalarType out_type = output_dtype.value();
-    TORCH_CHECK(out_type == at::kBFloat16 || out_type == at::kHalf || out_type == at::kInt,
-                "output_dtype of npu_quant_matmul should be bfloat16, float16 or int32, but it is ", out_type);
+    // output_dtype=None is the int8 (requantized) output, as for the operator this signature comes from
+    const at::ScalarType out_type = output_dtype.value_or(at::kChar);
+    TORCH_CHECK(out_type == at::kBFloat16 || out_type == at::kHalf || out_type == at::kInt || out_type == at::kChar,
+                "output_dtype of npu_quant_matmul should be int8, bfloat16, float16 or int32, but it is ", out_type);
+    const at::Tensor &offset_real = offset.value_or(at::Tensor());
+    TORCH_CHECK(!offset_real.defined() || out_type == at::kChar,
+                "npu_quant_matmul: offset only applies to an int8 output, but output_dtype is ", out_type);
     c10::cuda::CUDAGuard guard(x1.device());
 
     const int64_t K = x1.size(-1);
@@ -54,9 +52,9 @@ at::Tensor npu_quant_matmul(const at::Tensor &x1, const at::Tensor &x2, const at
     if (bias_real.defined()) {
         TORCH_CHECK(bias_real.numel() == N, "bias of npu_quant_matmul should have N=", N, " elements, but it has ",
                     bias_real.numel());
-        if (out_type == at::kInt) {
-            TORCH_CHECK(bias_real.scalar_type() == at::kInt, "bias must be int32 when output_dtype is int32, but it is ",
-                        bias_real.scalar_type());
+        if (out_type == at::kInt || out_type == at::kChar) {
+            TORCH_CHECK(bias_real.scalar_type() == at::kInt, "bias must be int32 when output_dtype is int32 or int8, "
+                        "but it is ", bias_real.scalar_type());
         } else {
             TORCH_CHECK(bias_real.scalar_type() == at::kBFloat16 || bias_real.scalar_type() == at::kHalf ||
                             bias_real.scalar_type() == at::kFloat,
@@ -86,6 +84,27 @@ at::Tensor npu_quant_matmul(const at::Tensor &x1, const at::Tensor &x2, const at
     at::Tensor pertoken_c = pertoken_real.defined() ? pertoken_real.contiguous() : pertoken_real;
     at::Tensor bias_c = bias_real.defined() ? bias_real.contiguous() : bias_real;
 
+    if (out_type == at::kChar) {
+        if (offset_real.defined()) {
+            TORCH_CHECK(offset_real.scalar_type() == at::kFloat && (offset_real.numel() == N || offset_real.numel() == 1),
+                        "offset of npu_quant_matmul should be float32 with N=", N, " elements or one, but it is ",
+                        offset_real.scalar_type(), " with ", offset_real.numel());
+        }
+        at::Tensor offset_c = offset_real.defined() ? offset_real.contiguous() : offset_real;
+        size_t ws_size = 0;
+        EXEC_QMM_CMD(qmm_quant_matmul_int8_workspace_size, M, N, K, &ws_size);
+        at::Tensor ws = op_plugin_utils::qmm_workspace(a, ws_size, /*family=*/3);
+        EXEC_QMM_CMD(qmm_quant_matmul_int8, static_cast<const int8_t *>(a.const_data_ptr()), std::max<int64_t>(K, 1),
+                     static_cast<const int8_t *>(b.const_data_ptr()), stride_k, stride_n,
+                     static_cast<const float *>(scale_c.const_data_ptr()), scale_c.numel(),
+                     static_cast<const float *>(op_plugin_utils::opt_ptr(offset_c)),
+                     offset_c.defined() ? offset_c.numel() : 0,
+                     static_cast<const float *>(op_plugin_utils::opt_ptr(pertoken_c)),
+                     static_cast<const int32_t *>(op_plugin_utils::opt_ptr(bias_c)),
+                     static_cast<int8_t *>(result.data_ptr()), N, M, N, K, ws.defined() ? ws.data_ptr() : nullptr,
+                     ws_size, op_plugin_utils::current_stream(a));
+        return result;
+    }
     size_t workspace_size = 0;
     EXEC_QMM_CMD(qmm_quant_matmul_workspace_size, M, N, K, QMM_ALGO_AUTO, &workspace_size);
     at::Tensor workspace = op_plugin_utils::qmm_workspace(a, workspace_size);

@@ -149,6 +149,23 @@ QMM_API int qmm_quant_matmul(const int8_t *x1, int64_t ld_x1, const int8_t *x2, 
                              void *workspace, size_t workspace_bytes, void *stream);
 
 /*
+ * W8A8 matmul with an int8 (requantized) output: torch op `npu_quant_matmul` with output_dtype = int8 and the
+ * optional `offset` (neither the operator nor this arithmetic is in the reference snapshot; the form is this
+ * library's stated choice):
+ *   acc = x1 @ x2 + bias (int32, exact);  v = float(acc) * scale[n] (* pertoken_scale[m]) (+ offset[n])  in fp32,
+ *   one rounding per operation;  out = clamp(rint(v), -128, 127), ties to even.
+ * scale / offset: fp32 with N elements or one; offset, pertoken_scale and bias (int32 [N]) may be NULL.
+ * workspace: 256-byte aligned, qmm_quant_matmul_int8_workspace_size bytes; it holds the matmul kernels' own
+ * scratch (cleared by the call) and the int32 accumulator, and needs no preparation by the caller.
+ */
+QMM_API int qmm_quant_matmul_int8_workspace_size(int64_t M, int64_t N, int64_t K, size_t *bytes);
+QMM_API int qmm_quant_matmul_int8(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_stride_k,
+                                  int64_t x2_stride_n, const float *scale, int64_t scale_len, const float *offset,
+                                  int64_t offset_len, const float *pertoken_scale, const int32_t *bias, int8_t *out,
+                                  int64_t ld_out, int64_t M, int64_t N, int64_t K, void *workspace,
+                                  size_t workspace_bytes, void *stream);
+
+/*
  * Decode-shape W8A8 matmul that allocates nothing.  It has no counterpart in
  * the reference: it exists for hosts that may not call cudaMalloc (or any
  * allocator) once they are running — a server whose device memory was split up

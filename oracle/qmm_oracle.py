@@ -170,9 +170,20 @@ def quant_matmul(x1, x2, scale, *, offset=None, pertoken_scale=None, bias=None, 
     (test/test_custom_ops/test_mm_reduce_scatter_base.py:74,79); the integer
     product is evaluated exactly instead of in fp32.
     """
-    if offset is not None:
-        raise NotImplementedError("offset is only meaningful for an int8 output, which no configuration uses")
+    if offset is not None and output_dtype != torch.int8:
+        raise ValueError("offset only applies to an int8 output")
     acc = int8_matmul_exact(x1, x2)
+    if output_dtype == torch.int8:
+        # requantized output (this build's stated choice; the operator is not in the reference snapshot):
+        # v = float(acc + bias) * scale[n] (* pertoken[m]) (+ offset[n]) in fp32, one rounding per operation,
+        # then round half to even and clamp to [-128, 127]
+        if bias is not None:
+            acc = acc + bias.cpu().numpy().astype(np.int32)[None, :]
+        v = dequant_epilogue_f32(acc, scale, pertoken_scale, None)
+        if offset is not None:
+            o = _f32(offset).reshape(-1)
+            v = (v + (o[None, :] if o.size > 1 else o[0])).astype(np.float32)
+        return torch.from_numpy(np.clip(np.rint(v), -128, 127).astype(np.int8))
     if output_dtype == torch.int32:
         if bias is not None:
             acc = acc + bias.cpu().numpy().astype(np.int32)[None, :]

@@ -90,7 +90,7 @@ def test_argument_checks(torch_npu, dev):
     with pytest.raises(RuntimeError, match="offset"):
         torch_npu.npu_quant_matmul(q, w, s, offset=torch.zeros(32, device=dev), output_dtype=torch.bfloat16)
     with pytest.raises(RuntimeError, match="output_dtype"):
-        torch_npu.npu_quant_matmul(q, w, s)
+        torch_npu.npu_quant_matmul(q, w, s, output_dtype=torch.float32)
     with pytest.raises(RuntimeError, match="pertoken_scale"):
         torch_npu.npu_quant_matmul(q, w, s, pertoken_scale=torch.ones(5, device=dev), output_dtype=torch.bfloat16)
     with pytest.raises(RuntimeError, match="bfloat16 or float16"):
@@ -127,3 +127,21 @@ def test_weight_quant_batchmatmul_prepack_cache(torch_npu, capi, oracle, dev):
     x5, w5, s5, o5 = oracle.make_w4a16_inputs(16, 512, 256, seed=11, group=64)
     y5 = torch_npu.npu_weight_quant_batchmatmul(x5.to(dev), w5.to(dev), s5.to(dev), o5.to(dev), antiquant_group_size=64)
     assert torch.equal(y5, capi.weight_quant_batchmatmul(x5.to(dev), w5.to(dev), s5.to(dev), o5.to(dev), group_size=64))
+
+
+def test_quant_matmul_int8_output_and_offset(torch_npu, oracle, dev):
+    """output_dtype=None (or torch.int8) is the requantized int8 output; offset applies to it alone."""
+    g = torch.Generator().manual_seed(5)
+    x1 = torch.randint(-127, 128, (2, 9, 256), generator=g, dtype=torch.int8)
+    x2 = torch.randint(-127, 128, (256, 136), generator=g, dtype=torch.int8)
+    scale = torch.empty(136).uniform_(1e-4, 4e-4, generator=g)
+    offset = torch.empty(136).uniform_(-10, 10, generator=g)
+    want = oracle.quant_matmul(x1.reshape(18, 256), x2, scale, offset=offset, output_dtype=torch.int8).reshape(2, 9, 136)
+    got = torch_npu.npu_quant_matmul(x1.to(dev), x2.to(dev), scale.to(dev), offset=offset.to(dev))
+    assert got.dtype == torch.int8 and got.shape == (2, 9, 136) and torch.equal(got.cpu(), want)
+    got2 = torch_npu.npu_quant_matmul(x1.to(dev), x2.to(dev), scale.to(dev), offset=offset.to(dev),
+                                      output_dtype=torch.int8)
+    assert torch.equal(got2, got)
+    with pytest.raises(RuntimeError, match="offset only applies to an int8 output"):
+        torch_npu.npu_quant_matmul(x1.to(dev), x2.to(dev), scale.to(dev), offset=offset.to(dev),
+                                   output_dtype=torch.bfloat16)

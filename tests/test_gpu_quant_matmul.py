@@ -211,3 +211,27 @@ def test_decode_full_size(capi, oracle, dev, M, KN):
     y_ref = oracle.quant_matmul(a.cpu(), w_cols, scale[cols].cpu(), pertoken_scale=pt.cpu(),
                                 output_dtype=torch.bfloat16)
     assert oracle.bf16_ulp_distance(y[:, cols].cpu(), y_ref).max().item() <= ULP_TOL
+
+
+@pytest.mark.parametrize("shape", [(128, 1024, 1024), (1, 512, 264), (33, 4096, 520), (300, 257, 130), (2048, 2048, 1024)])
+def test_int8_requantized_output(capi, oracle, dev, shape):
+    """output_dtype = int8 with offset, per-token scale and int32 bias: bit-exact against the oracle's stated
+    arithmetic (fp32, one rounding per operation, ties to even, saturation), for both weight layouts; two
+    shapes in a row share the scratch."""
+    M, K, N = shape
+    g = torch.Generator().manual_seed(M + K + N)
+    x1 = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8)
+    x2 = torch.randint(-127, 128, (K, N), generator=g, dtype=torch.int8)
+    scale = torch.empty(N).uniform_(2e-5, 2e-4, generator=g)
+    offset = torch.empty(N).uniform_(-20, 20, generator=g)
+    pt = torch.empty(M).uniform_(0.5, 2.0, generator=g)
+    bias = torch.randint(-1000, 1000, (N,), generator=g, dtype=torch.int32)
+    for kw in (dict(offset=offset, pertoken_scale=pt, bias=bias), dict(), dict(offset=offset[:1])):
+        want = oracle.quant_matmul(x1, x2, scale, output_dtype=torch.int8, **kw)
+        got = capi.quant_matmul_int8(x1.to(dev), x2.to(dev), scale.to(dev),
+                                     **{k: v.to(dev) for k, v in kw.items()})
+        assert got.dtype == torch.int8 and torch.equal(got.cpu(), want)
+        assert want.min().item() == -128 or want.max().item() == 127 or M * N < 1000  # the clamp is exercised
+    wt = x2.t().contiguous().to(dev)
+    got_t = capi.quant_matmul_int8(x1.to(dev), wt.t(), scale.to(dev), offset=offset.to(dev))
+    assert torch.equal(got_t.cpu(), oracle.quant_matmul(x1, x2, scale, offset=offset, output_dtype=torch.int8))
