@@ -375,6 +375,13 @@ def run_prefill(args, pkg, dev):
     for L in layers:
         L["q"], L["s"] = capi.dynamic_quant(L["x"])
     sustained = None
+    if args.quick:
+        roofline["sustained"] = None
+        print(json.dumps({"metric": "W8A8 GEMM TOPS", "value": value, "unit": "TOPS", "n_gpus": 1, "steps": args.steps,
+                          "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "config": prefill_config(),
+                          "clocks": clocks.summary(), "gpu_launches": 8 * args.steps, "roofline": roofline,
+                          "quick": True}), flush=True)
+        return
     try:
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -766,6 +773,22 @@ def run_case(args):
     elif args.case == "dynamic_quant":
         xs = [torch.randn((M, K), device=dev, dtype=torch.bfloat16) for _ in range(nb)]
         fn = lambda i: capi.dynamic_quant(xs[i % nb])  # noqa: E731
+    elif args.case == "dense_matmul":
+        # the bf16 matmul of npu_mm_reduce_scatter_base / npu_all_gather_base_mm, through a one-rank communicator
+        import ctypes
+
+        uid = ctypes.create_string_buffer(capi.UNIQUE_ID_BYTES)
+        capi.check(capi.lib().qmm_comm_unique_id(uid), "qmm_comm_unique_id")
+        capi.check(capi.lib().qmm_comm_init_rank(b"bench_solo", uid, 1, 0), "qmm_comm_init_rank")
+        a = torch.randn((M, K), device=dev, dtype=torch.bfloat16)
+        ws = [torch.randn((K, N), device=dev, dtype=torch.bfloat16) for _ in range(nb)]
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        st = torch.cuda.current_stream
+
+        def fn(i):
+            capi.check(capi.lib().qmm_mm_reduce_scatter(a.data_ptr(), capi.DTYPE_BF16, K, ws[i % nb].data_ptr(), N, 1, None,
+                                                        out.data_ptr(), N, M, N, K, b"bench_solo", b"sum", 0, None, 0,
+                                                        st().cuda_stream), "qmm_mm_reduce_scatter")
     elif args.case == "rms_norm_quant":
         xs = [torch.randn((M, K), device=dev, dtype=torch.bfloat16) for _ in range(nb)]
         gamma = torch.randn(K, device=dev, dtype=torch.bfloat16)
@@ -800,7 +823,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--case", default=None, choices=["quant_matmul", "dynamic_quant", "w4a16", "w4a16_prepacked",
-                                                     "rms_norm_quant"],
+                                                     "rms_norm_quant", "dense_matmul"],
                     help="run one kernel a few times (profiling target) instead of the benchmark")
     ap.add_argument("--M", type=int, default=8192)
     ap.add_argument("--K", type=int, default=4096)
@@ -809,6 +832,9 @@ def main():
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--buffers", type=int, default=1, help="--case: rotate over this many weight/input buffers")
     ap.add_argument("--graph", action="store_true", help="--case: also time the launches replayed from a CUDA graph")
+    ap.add_argument("--quick", action="store_true",
+                    help="N = 1: headline step and roofline only (no sustained loop, extras, end-to-end or CPU legs); "
+                         "what the launch list under profiles/ was captured on")
     args = ap.parse_args()
     if args.case is not None:
         run_case(args)
