@@ -142,7 +142,7 @@ def lib() -> ctypes.CDLL:
         L.qmm_comm_register.argtypes = [c.c_char_p, c.c_void_p, c.c_int, c.c_int]
         L.qmm_comm_info.argtypes = [c.c_char_p, c.POINTER(c.c_int), c.POINTER(c.c_int)]
         L.qmm_comm_destroy.argtypes = [c.c_char_p]
-        L.qmm_comm_stats.argtypes = [c.c_char_p, c.POINTER(c.c_int64), c.POINTER(c.c_int64), c.POINTER(c.c_int64)]
+        L.qmm_comm_stats.argtypes = [c.c_char_p] + [c.POINTER(c.c_int64)] * 4
         L.qmm_comm_stats.restype = c.c_int
         L.qmm_comm_peer_memory_size.argtypes = [c.c_int64, c.c_int64, c.c_int, c.POINTER(c.c_size_t)]
         L.qmm_comm_attach_peer_memory.argtypes = [c.c_char_p, c.POINTER(c.c_void_p), c.c_void_p, c.c_size_t]
@@ -365,9 +365,10 @@ def rms_norm_dynamic_quant(x: torch.Tensor, gamma: torch.Tensor, epsilon: float 
 
 def comm_stats(name: str) -> dict:
     """How many qmm_mm_all_reduce calls of communicator `name` took which allreduce path."""
-    a, b, c = ctypes.c_int64(0), ctypes.c_int64(0), ctypes.c_int64(0)
-    check(lib().qmm_comm_stats(name.encode(), ctypes.byref(a), ctypes.byref(b), ctypes.byref(c)), "qmm_comm_stats")
-    return {"peer_calls": a.value, "peer_pushed_calls": b.value, "nccl_calls": c.value}
+    a, b, f, c = ctypes.c_int64(0), ctypes.c_int64(0), ctypes.c_int64(0), ctypes.c_int64(0)
+    check(lib().qmm_comm_stats(name.encode(), ctypes.byref(a), ctypes.byref(b), ctypes.byref(f), ctypes.byref(c)),
+          "qmm_comm_stats")
+    return {"peer_calls": a.value, "peer_pushed_calls": b.value, "peer_fused_calls": f.value, "nccl_calls": c.value}
 
 
 def int8_mma_peak(batches: int = 1024) -> dict:

@@ -27,6 +27,7 @@
 
 #include "dense_gemm.cuh"
 #include "peer_all_reduce.cuh"
+#include "peer_fused.cuh"
 #include "peer_scatter_gather.cuh"
 #include "qmm_common.cuh"
 #include "w8a8_epilogue.cuh"
@@ -132,6 +133,7 @@ struct PeerMem {
     uint32_t epoch = 0;   // number of collective calls made through the regions
     uint32_t rs_calls = 0;  // reduce-scatter / all-gather calls so far (targets of their CTA counters)
     uint32_t ag_calls = 0;
+    uint64_t fused_clean_gen = 0;  // device_status_generation() when the fused kernel's counters were last cleared
 };
 
 struct Comm {
@@ -143,6 +145,7 @@ struct Comm {
     bool owned = false;
     int64_t stat_peer = 0;         // calls whose allreduce ran in the library's own kernel over peer memory
     int64_t stat_peer_pushed = 0;  // ... of which the matmul delivered its tiles to the owners itself
+    int64_t stat_peer_fused = 0;   // ... of which the matmul kernel also reduced and gathered (no second kernel)
     int64_t stat_nccl = 0;         // calls whose allreduce NCCL carried
     cudaStream_t stream = nullptr;  // communication stream
     cudaEvent_t chunk_ready[kMaxChunks] = {};
@@ -296,6 +299,26 @@ bool push_disabled() {
     return off;
 }
 
+// QMM_PEER_FUSED=0 keeps the reduce + gather in a kernel of its own behind the matmul.
+bool fused_disabled() {
+    static const bool off = [] {
+        const char *e = getenv("QMM_PEER_FUSED");
+        return e != nullptr && std::string(e) == "0";
+    }();
+    return off;
+}
+
+// Column chunks of the fused kernel (QMM_PEER_FUSED_CHUNKS, 1..8): what is left to exchange when the matmul
+// ends is one chunk; every chunk costs a round of flags.
+int fused_chunks() {
+    static const int n = [] {
+        const char *e = getenv("QMM_PEER_FUSED_CHUNKS");
+        const int v = e ? atoi(e) : 4;
+        return v < 1 ? 1 : (v > kFusedMaxChunks ? kFusedMaxChunks : v);
+    }();
+    return n;
+}
+
 bool peer_path_disabled() {
     static const bool off = [] {
         const char *e = getenv("QMM_ALLREDUCE");
@@ -358,7 +381,8 @@ extern "C" int qmm_comm_info(const char *name, int *nranks, int *rank) {
     return QMM_OK;
 }
 
-extern "C" int qmm_comm_stats(const char *name, int64_t *peer_calls, int64_t *peer_pushed_calls, int64_t *nccl_calls) {
+extern "C" int qmm_comm_stats(const char *name, int64_t *peer_calls, int64_t *peer_pushed_calls,
+                              int64_t *peer_fused_calls, int64_t *nccl_calls) {
     using namespace qmm;
     QMM_REQUIRE(name != nullptr, "qmm_comm_stats: name is NULL");
     std::lock_guard<std::mutex> lock(g_comm_mutex);
@@ -367,6 +391,7 @@ extern "C" int qmm_comm_stats(const char *name, int64_t *peer_calls, int64_t *pe
         return fail(QMM_ERR_NOT_FOUND, std::string("communicator '") + name + "' is not registered");
     if (peer_calls) *peer_calls = it->second.stat_peer;
     if (peer_pushed_calls) *peer_pushed_calls = it->second.stat_peer_pushed;
+    if (peer_fused_calls) *peer_fused_calls = it->second.stat_peer_fused;
     if (nccl_calls) *nccl_calls = it->second.stat_nccl;
     return QMM_OK;
 }
@@ -487,8 +512,20 @@ extern "C" int qmm_mm_all_reduce(const int8_t *x1, int64_t ld_x1, const int8_t *
             ep.ld_out = N;
             ep.M = rows;
             ep.N = N;
-            // the CTA-pair matmul stores each output tile into the region of the rank that owns its rows
+            // The epoch is drawn before the matmul (a fused launch raises flags itself) and given back if nothing
+            // was launched: a call that fails has touched no flag, so the ranks' epochs stay in step as long as
+            // every rank either launches or fails before launching.
+            {
+                std::lock_guard<std::mutex> lock(g_comm_mutex);
+                auto it = g_comms.find(hcom);
+                if (it == g_comms.end())
+                    return fail(QMM_ERR_NOT_FOUND, std::string("communicator '") + hcom + "' is not registered");
+                pp.epoch = ++it->second.peer.epoch;
+            }
+            // the CTA-pair matmul stores each output tile into the region of the rank that owns its rows, and
+            // (plain peer loads, one chunk of rows) reduces and gathers finished column chunks itself
             PushSpec spec;
+            FusedComm fspec;
             LaunchOptions opts;
             if (push_ok) {
                 for (int r = 0; r < kPeerMaxRanks; ++r) spec.base[r] = c.peer.base[r];
@@ -497,24 +534,59 @@ extern "C" int qmm_mm_all_reduce(const int8_t *x1, int64_t ld_x1, const int8_t *
                 spec.rank = c.rank;
                 spec.rows_per = pp.rows_per;
                 opts.push = &spec;
+                if (pp.mc_base == nullptr && !fused_disabled()) {
+                    for (int r = 0; r < kPeerMaxRanks; ++r) fspec.base[r] = c.peer.base[r];
+                    fspec.world = c.nranks;
+                    fspec.rank = c.rank;
+                    fspec.epoch = pp.epoch;
+                    fspec.chunks = fused_chunks();
+                    fspec.M = rows;
+                    fspec.N = N;
+                    fspec.rows_per = pp.rows_per;
+                    fspec.partial_off = pp.partial_off;
+                    fspec.red_off = pp.red_off;
+                    fspec.out = pp.out;
+                    fspec.status = pp.status;
+                    fspec.status_at_launch = pp.status_at_launch;
+                    fspec.enabled = 0;
+                    // arrival counters of the fused kernel: zero unless a call was cut short (or never used yet)
+                    {
+                        const uint64_t gen = device_status_generation();
+                        bool clean = false;
+                        {
+                            std::lock_guard<std::mutex> lock(g_comm_mutex);
+                            auto it = g_comms.find(hcom);
+                            if (it != g_comms.end()) {
+                                clean = it->second.peer.fused_clean_gen == gen;
+                                it->second.peer.fused_clean_gen = gen;
+                            }
+                        }
+                        if (!clean)
+                            QMM_CUDA_OK(cudaMemsetAsync(c.peer.base[c.rank] + kFusedFlagOffset + kFusedPushCountOffset, 0,
+                                                        kFusedCounterBytes, s));
+                    }
+                    fspec.debug = getenv("QMM_FUSED_DBG") ? atoi(getenv("QMM_FUSED_DBG")) : 0;
+                    opts.fused = &fspec;
+                }
             }
             rc = quant_matmul_dispatch(x1 + m0 * ld_x1, ld_x1, x2, x2_stride_k, x2_stride_n, ep, out_dtype, K,
                                        K == 0 ? QMM_ALGO_SIMT : QMM_ALGO_AUTO, workspace, workspace_bytes, s, &opts);
             pp.pushed = opts.push_applied ? 1 : 0;
-            if (rc != QMM_OK) return rc;
-            // The epoch advances only now: a call that failed before this point has touched no flag, so the
-            // ranks' epochs stay in step as long as every rank either launches or fails before launching.
             {
                 std::lock_guard<std::mutex> lock(g_comm_mutex);
                 auto it = g_comms.find(hcom);
-                if (it == g_comms.end())
-                    return fail(QMM_ERR_NOT_FOUND, std::string("communicator '") + hcom + "' is not registered");
-                pp.epoch = ++it->second.peer.epoch;
-                if (ci == 0) {
-                    ++it->second.stat_peer;
-                    if (pp.pushed) ++it->second.stat_peer_pushed;
+                if (it != g_comms.end()) {
+                    if (rc != QMM_OK) {
+                        --it->second.peer.epoch;
+                    } else if (ci == 0) {
+                        ++it->second.stat_peer;
+                        if (pp.pushed) ++it->second.stat_peer_pushed;
+                        if (opts.fused_applied) ++it->second.stat_peer_fused;
+                    }
                 }
             }
+            if (rc != QMM_OK) return rc;
+            if (opts.fused_applied) continue;  // the matmul kernel has done the exchange
             cudaStream_t ks = s;
             if (chunks > 1) {
                 QMM_CUDA_OK(cudaEventRecord(c.chunk_ready[ci], s));

@@ -79,7 +79,7 @@ __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
 // several times.
 // A wait also gives up when the process-wide status word changes while it polls (some kernel of this process
 // recorded a timeout): compared with the value at launch, so that an old, unread code does not abort later calls.
-__device__ __noinline__ bool peer_wait_flag(const uint32_t *flag, uint32_t epoch, uint32_t *status, uint32_t status0,
+static __device__ __noinline__ bool peer_wait_flag(const uint32_t *flag, uint32_t epoch, uint32_t *status, uint32_t status0,
                                             uint32_t where) {
     if (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) >= 0) return true;
     const uint64_t t0 = globaltimer_ns();

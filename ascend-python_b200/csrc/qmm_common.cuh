@@ -38,6 +38,8 @@ int fail(int code, const std::string &msg);
 uint32_t *device_status_word();
 // Host-side view of that word without creating it (0 if it does not exist yet); `clear` resets it.
 uint32_t device_status_peek(bool clear);
+// moves whenever a non-zero status word is cleared (see qmm_runtime.cu)
+uint64_t device_status_generation();
 
 // Number of SMs of the current device (cached per device).
 int sm_count();

@@ -46,13 +46,25 @@ uint32_t *device_status_word() {
     return g_status_dev;
 }
 
+// Counts the times a non-zero status word was cleared: device-side state that a kernel leaves behind only
+// when it completes (arrival counters) is cleaned by its owner when this number has moved.
+static uint64_t g_status_generation = 1;
+
 // Current value of the status word as the host sees it (0 if it was never created); `clear` resets it.
 uint32_t device_status_peek(bool clear) {
     std::lock_guard<std::mutex> lock(g_mutex);
     if (g_status_host == nullptr) return 0;
     const uint32_t v = *reinterpret_cast<volatile uint32_t *>(g_status_host);
-    if (clear && v != 0) *reinterpret_cast<volatile uint32_t *>(g_status_host) = 0;
+    if (clear && v != 0) {
+        *reinterpret_cast<volatile uint32_t *>(g_status_host) = 0;
+        ++g_status_generation;
+    }
     return v;
+}
+
+uint64_t device_status_generation() {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    return g_status_generation;
 }
 
 int sm_count() {
@@ -118,7 +130,10 @@ int qmm_device_status(int reset) {
     std::lock_guard<std::mutex> lock(qmm::g_mutex);
     if (qmm::g_status_host == nullptr) return 0;
     int v = static_cast<int>(*reinterpret_cast<volatile uint32_t *>(qmm::g_status_host));
-    if (reset) *reinterpret_cast<volatile uint32_t *>(qmm::g_status_host) = 0;
+    if (reset && v != 0) {
+        *reinterpret_cast<volatile uint32_t *>(qmm::g_status_host) = 0;
+        ++qmm::g_status_generation;
+    }
     return v;
 }
 }

@@ -32,11 +32,14 @@ struct PushSpec {
     int world, rank;
     int64_t rows_per;  // a multiple of 32, so the 32 rows of an epilogue warp have one owner
 };
+struct FusedComm;  // peer_fused.cuh
 // What a caller of quant_matmul_dispatch may ask of the launch beyond the problem itself.
 struct LaunchOptions {
     int sm_reserve = 0;              // SMs the persistent kernels leave idle (a collective runs beside them)
     const PushSpec *push = nullptr;  // owners' receive areas for the output tiles (CTA-pair kernel only)
     bool push_applied = false;       // out: the launch did deliver its tiles to the owners
+    const FusedComm *fused = nullptr;  // allreduce inside the CTA-pair kernel (needs push)
+    bool fused_applied = false;      // out: the launch reduces and gathers the output itself
 };
 // Kernel-side form: one output tensor map per owner.
 struct PushMaps {

@@ -14,8 +14,13 @@
 //   tmem_full[b]  one per CTA; the leader's tcgen05.commit arrives on both
 //   tmem_empty[b] leader's barrier; the 4+4 epilogue warps of the pair arrive on it
 // No TMA load uses multicast; every wait is bounded (see mbar_wait).
+//
+// FUSED (the row-parallel matmul + allreduce): four more warps per CTA reduce and gather finished column
+// chunks over peer memory while the matmul goes on; tiles are then visited chunk by chunk, and within a
+// chunk every rank starts with the rows of its right-hand neighbour so that the owners' links fill evenly.
 #include <cstring>
 
+#include "peer_fused.cuh"
 #include "qmm_common.cuh"
 #include "w8a8_epilogue.cuh"
 
@@ -32,6 +37,8 @@ constexpr int kPAStageBytes = kPM * kPK;
 constexpr int kPBStageBytes = (kPN / 2) * kPK;
 constexpr int kPStageBytes = kPAStageBytes + kPBStageBytes;  // per CTA
 constexpr int kPThreads = 192;
+constexpr int kPFusedThreads = kPThreads + kFusedThreads;
+static_assert(kPN == kFusedTileCols, "the communication warps cut the output into the matmul's tile columns");
 constexpr uint32_t kPTmemCols = 512;
 constexpr int kPEpiWarps = 4;
 constexpr int kPEpiStageBytes = 2 * 4096;
@@ -44,6 +51,7 @@ struct PairSmemTail {
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
     uint32_t abort_flag;
+    uint32_t comm_ok;
 };
 
 constexpr size_t kPairSmemBytes = kPStages * kPStageBytes + kPEpiWarps * kPEpiStageBytes +
@@ -73,6 +81,22 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tile
         n_blk = first_n + r % cols;
         m_blk = r / cols;
     }
+}
+
+// Tile order of the fused kernel: column chunk by column chunk; inside a chunk the order above (`raster`
+// chosen for a chunk's width), with the tile rows rotated by m_rot (the first tile row of the right-hand
+// neighbour's rows) so that the ranks do not all push to the same owner at the same time.
+__device__ __forceinline__ void fused_tile_coords(int tile, int tiles_m, int tiles_n, int chunks, int raster, int m_rot,
+                                                  int &m_blk, int &n_blk, int &chunk) {
+    int c = 0;
+    while (c + 1 < chunks && tile >= fused_chunk_first(tiles_n, chunks, c + 1) * tiles_m) ++c;
+    const int nb0 = fused_chunk_first(tiles_n, chunks, c);
+    const int ncols = fused_chunk_first(tiles_n, chunks, c + 1) - nb0;
+    int m, n;
+    pair_tile_coords(tile - nb0 * tiles_m, tiles_m, ncols, raster, m, n);
+    n_blk = nb0 + n;
+    m_blk = (m_rot + m) % tiles_m;
+    chunk = c;
 }
 
 // Chooses the order that moves fewer bytes from DRAM.  With g tile rows (or columns) per group the
@@ -110,11 +134,12 @@ int pair_choose_raster(int64_t M, int64_t N, int64_t K, int64_t out_elt, int wav
     return best;
 }
 
-template <typename OutT, bool B_MN_MAJOR>
-__global__ void __launch_bounds__(kPThreads, 1)
+template <typename OutT, bool B_MN_MAJOR, bool FUSED>
+__global__ void __launch_bounds__(FUSED ? kPFusedThreads : kPThreads, 1)
 w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ PushMaps push,
-                 EpilogueParams ep, int K, int use_tma_store, int raster, uint32_t *status) {
+                 const __grid_constant__ FusedComm fc, EpilogueParams ep, int K, int use_tma_store, int raster,
+                 uint32_t *status) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t smem_base = smem_u32(smem_raw);
     const uint32_t cta_rank = cluster_ctarank();  // 0 = leader
@@ -137,6 +162,18 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int num_kb = (K + kPK - 1) / kPK;
     const int pair_id = blockIdx.x >> 1;
     const int num_pairs = gridDim.x >> 1;
+    // fused: first tile row of the right-hand neighbour's rows
+    const int m_rot = (FUSED && !(fc.debug & 2)) ? static_cast<int>((static_cast<int64_t>((fc.rank + 1) % fc.world) * fc.rows_per / (2 * kPM)) %
+                                               tiles_m)
+                            : 0;
+    auto tile_coords = [&](int tile, int &m_blk, int &n_blk, int &chunk) {
+        if constexpr (FUSED) {
+            fused_tile_coords(tile, tiles_m, tiles_n, fc.chunks, raster, m_rot, m_blk, n_blk, chunk);
+        } else {
+            pair_tile_coords(tile, tiles_m, tiles_n, raster, m_blk, n_blk);
+            chunk = 0;
+        }
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kPStages; ++s) {
@@ -169,8 +206,8 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         uint32_t stage = 0, phase = 0;
         bool ok = true;
         for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
-            int m_blk, n_blk;
-            pair_tile_coords(tile, tiles_m, tiles_n, raster, m_blk, n_blk);
+            int m_blk, n_blk, chunk;
+            tile_coords(tile, m_blk, n_blk, chunk);
             const int m0 = m_blk * 2 * kPM + static_cast<int>(cta_rank) * kPM;
             const int n0 = n_blk * kPN + static_cast<int>(cta_rank) * (kPN / 2);
             for (int kb = 0; kb < num_kb; ++kb) {
@@ -240,6 +277,10 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 if (ok) tc_commit_pair_warp(smem_u32(&tail->tmem_full[buf]), 0x3);
             }
         }
+    } else if (FUSED && warp >= kPThreads / 32) {
+        // ---------------- communication warps (both CTAs; fused kernel only) ----------------
+        if constexpr (FUSED)
+            fused_comm_role<OutT>(fc, static_cast<int>(threadIdx.x) - kPThreads, &tail->comm_ok);
     } else {
         // ---------------- epilogue warps (both CTAs) ----------------
         const int quarter = warp & 3;
@@ -249,9 +290,22 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         int local = 0;
         bool ok = true;
         if (lane == 0 && use_tma_store) tma_prefetch_desc(&tmap_out);
+        // fused: tiles of the chunk this warp is in whose stores it has issued
+        int cur_chunk = -1;
+        uint32_t units = 0;
+        auto chunk_expected = [&](int c) {
+            return static_cast<uint32_t>((fused_chunk_first(tiles_n, fc.chunks, c + 1) -
+                                          fused_chunk_first(tiles_n, fc.chunks, c)) * tiles_m * 2 * kPEpiWarps);
+        };
         for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++local) {
-            int m_blk, n_blk;
-            pair_tile_coords(tile, tiles_m, tiles_n, raster, m_blk, n_blk);
+            int m_blk, n_blk, chunk;
+            tile_coords(tile, m_blk, n_blk, chunk);
+            if (FUSED && chunk != cur_chunk) {
+                if (cur_chunk >= 0 && lane == 0 && !(fc.debug & 4))
+                    fused_chunk_pushed(fc, cur_chunk, units, chunk_expected(cur_chunk));
+                cur_chunk = chunk;
+                units = 0;
+            }
             const uint32_t buf = local & 1;
             const uint32_t buf_phase = (local >> 1) & 1;
             ok = mbar_wait(smem_u32(&tail->tmem_full[buf]), buf_phase, abort_flag, 0x24);
@@ -282,8 +336,11 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tail->tmem_empty[buf]), 0));
+            ++units;
         }
         if (lane == 0) tma_store_wait_all<0>();
+        // a warp that was cut short reports nothing: the peers' bounded waits then run out
+        if (FUSED && ok && cur_chunk >= 0 && lane == 0 && !(fc.debug & 4)) fused_chunk_pushed(fc, cur_chunk, units, chunk_expected(cur_chunk));
         __syncwarp();
     }
 
@@ -325,11 +382,9 @@ int launch_pair_t(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_
     const int tiles = static_cast<int>(((ep.M + 2 * kPM - 1) / (2 * kPM)) * ((ep.N + kPN - 1) / kPN));
     int pairs = (sm_count() - (opts != nullptr && opts->sm_reserve > 0 ? opts->sm_reserve : 0)) / 2;
     if (pairs < 1) pairs = 1;
+    const int pairs_all = pairs;
     if (tiles < pairs) pairs = tiles;
     uint32_t *status = device_status_word();
-    auto kern = mn_major ? w8a8_pair_kernel<OutT, true> : w8a8_pair_kernel<OutT, false>;
-    QMM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     static_cast<int>(kPairSmemBytes)));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
     cfg.blockDim = dim3(kPThreads);
@@ -342,7 +397,7 @@ int launch_pair_t(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const int raster = pair_choose_raster(ep.M, ep.N, K, static_cast<int64_t>(sizeof(OutT)), pairs);
+    int raster = pair_choose_raster(ep.M, ep.N, K, static_cast<int64_t>(sizeof(OutT)), pairs);
     PushMaps push;
     memset(&push, 0, sizeof(push));
     if (const PushSpec *ps = (opts != nullptr ? opts->push : nullptr)) {
@@ -366,8 +421,48 @@ int launch_pair_t(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_
             opts->push_applied = true;
         }
     }
-    QMM_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ta, tb, tout, push, ep, static_cast<int>(K), use_tma_store, raster,
-                                   status));
+    // The allreduce inside the kernel: only when the tiles are pushed, the whole GPU is one resident wave of
+    // CTAs (the communication warps of different CTAs count one another) and 32-bit vector indices suffice.
+    FusedComm fc;
+    memset(&fc, 0, sizeof(fc));
+    bool fused = false;
+    if constexpr (sizeof(OutT) == 2) {
+        if (opts != nullptr && opts->fused != nullptr && push.enabled && opts->sm_reserve == 0 &&
+            2 * pairs_all <= sm_count() && 2 * pairs_all >= 2 * (opts->fused->world - 1) && ep.N % 8 == 0) {
+            fc = *opts->fused;
+            const int tiles_m = static_cast<int>((ep.M + 2 * kPM - 1) / (2 * kPM));
+            const int tiles_n = static_cast<int>((ep.N + kPN - 1) / kPN);
+            if (fc.chunks > tiles_n) fc.chunks = tiles_n;
+            if (fc.chunks > kFusedMaxChunks) fc.chunks = kFusedMaxChunks;
+            if (fc.chunks < 1) fc.chunks = 1;
+            if (ep.M * ep.N < (1ll << 33)) {
+                // the order inside a chunk: as for a matmul of the chunk's width
+                const int64_t chunk_cols = static_cast<int64_t>((tiles_n + fc.chunks - 1) / fc.chunks) * kPN;
+                raster = pair_choose_raster(ep.M, chunk_cols < ep.N ? chunk_cols : ep.N, K,
+                                            static_cast<int64_t>(sizeof(OutT)), pairs_all);
+                fc.enabled = 1;
+                fused = true;
+                opts->fused_applied = true;
+            }
+        }
+    }
+    if (fused) {
+        if constexpr (sizeof(OutT) == 2) {
+            auto kern = mn_major ? w8a8_pair_kernel<OutT, true, true> : w8a8_pair_kernel<OutT, false, true>;
+            QMM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(kPairSmemBytes)));
+            cfg.blockDim = dim3(kPFusedThreads);
+            cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs_all));  // also the CTAs without a tile communicate
+            QMM_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ta, tb, tout, push, fc, ep, static_cast<int>(K), use_tma_store,
+                                           raster, status));
+        }
+    } else {
+        auto kern = mn_major ? w8a8_pair_kernel<OutT, true, false> : w8a8_pair_kernel<OutT, false, false>;
+        QMM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kPairSmemBytes)));
+        QMM_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ta, tb, tout, push, fc, ep, static_cast<int>(K), use_tma_store, raster,
+                                       status));
+    }
     return QMM_OK;
 }
 

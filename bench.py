@@ -732,14 +732,15 @@ def run_rowpar(args, pkg, dev, rank, world):
             "config": rowpar_config(world),
             "allreduce_path": dict(stats_timed, note="calls of npu_mm_all_reduce_base on rank 0 up to the end of the "
                                    "timed region and the parity step, counted by the library per path taken: its own "
-                                   "reduce+gather kernel over peer memory (of which: output tiles pushed to their "
-                                   "owners by the matmul's epilogue) or NCCL"),
+                                   "kernels over peer memory (of which: output tiles pushed to their owners by the "
+                                   "matmul's epilogue; of which: reduce + gather done by the matmul kernel's own "
+                                   "communication warps, no second kernel) or NCCL"),
             "parity": parity,
             "clocks": clocks.summary(),
             "e2e": {"value": total_ops * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS",
                     "h2d_bytes_per_step": host_x.numel() * 2, "d2h_bytes_per_step": host_y.numel() * 2,
                     "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
-            "gpu_launches": args.steps * 3,
+            "gpu_launches": args.steps * (2 if stats_timed["peer_fused_calls"] >= args.steps else 3),
             "roofline": {"bound": "tensor", "kernel": "w8a8_pair_kernel", "achieved": achieved, "peak": int8_peak,
                          "unit": "TFLOP/s", "frac": achieved / int8_peak, "traffic": None,
                          "peak_note": f"2 x {peaks['source']} sustained bf16 cuBLAS throughput"},

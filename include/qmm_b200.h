@@ -269,9 +269,11 @@ QMM_API int qmm_comm_register(const char *name, void *nccl_comm, int nranks, int
 QMM_API int qmm_comm_info(const char *name, int *nranks, int *rank);
 QMM_API int qmm_comm_destroy(const char *name);
 /* Calls of qmm_mm_all_reduce made through the communicator so far, by the path their allreduce took:
- * the library's own kernel over peer memory (and, of those, calls whose matmul pushed its output tiles to
- * the owning ranks itself), or NCCL.  Any pointer may be NULL.  No counterpart in the reference. */
-QMM_API int qmm_comm_stats(const char *name, int64_t *peer_calls, int64_t *peer_pushed_calls, int64_t *nccl_calls);
+ * the library's own kernels over peer memory (of those, calls whose matmul pushed its output tiles to the
+ * owning ranks itself; and, of those again, calls whose matmul kernel also reduced and gathered the output, so
+ * that no second kernel ran), or NCCL.  Any pointer may be NULL.  No counterpart in the reference. */
+QMM_API int qmm_comm_stats(const char *name, int64_t *peer_calls, int64_t *peer_pushed_calls,
+                           int64_t *peer_fused_calls, int64_t *nccl_calls);
 
 /* Peer memory for the allreduce of qmm_mm_all_reduce (no counterpart in the reference: its device
  * library owns the communication buffers behind the communicator name,

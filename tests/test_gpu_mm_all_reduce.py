@@ -142,17 +142,21 @@ def _rank_main(rank, world, port, shapes, c2p):
         for i, y in enumerate(outs):
             M, K, N = chain[i % 2]
             c2p.put((rank, ("chain", i, M, K, N), y.cpu(), None, None, _digest(y)))
+        from ascend_python_b200 import capi
+        c2p.put((rank, ("stats",), capi.comm_stats(hcom), None, None, ""))
         dist.barrier()
         torch_npu.destroy_comm(hcom)
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,path", [(2, "peer"), (2, "multimem"), (2, "nccl"), (4, "peer"), (4, "multimem"), (8, "peer"), (8, "multimem")])
+@pytest.mark.parametrize("world,path", [(2, "peer"), (2, "peer_unfused"), (2, "multimem"), (2, "nccl"), (4, "peer"),
+                                        (4, "multimem"), (8, "peer"), (8, "peer_unfused"), (8, "multimem")])
 def test_multi_rank(oracle, pkg, world, path):
-    """path "peer": the default (calls with comm_turn == 0 reduce and gather through peer memory in the
-    library's own kernel, plain peer loads); "multimem": the same with in-switch reduction / broadcast;
-    "nccl" forces NCCL for every call."""
+    """path "peer": the default (calls with comm_turn == 0 reduce and gather through peer memory with plain peer
+    loads: inside the matmul kernel for prefill shapes, in a kernel of its own otherwise); "peer_unfused": always
+    in a kernel of its own; "multimem": the same with in-switch reduction / broadcast; "nccl" forces NCCL for
+    every call."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
@@ -161,21 +165,24 @@ def test_multi_rank(oracle, pkg, world, path):
     # the last shape needs larger peer regions than the first ones allocated: the regions are re-made
     shapes = [(256, 1024, 512, 0), (2048, 4096, 1024, 2), (1000, 2048, 768, 3), (1000, 2048, 768, 0),
               (2048, 4096, 1024, 0), (3, 512, 264, 0), (4096, 512, 4352, 0)]
-    if path == "peer":
+    if path in ("peer", "peer_unfused"):
         shapes.append((4096, 28672, 8192, 0))  # the row-parallel benchmark configuration itself, at full size
     ctx = mp.get_context("spawn")
     c2p = ctx.Queue()
     port = 29700 + os.getpid() % 1000
     env = dict(os.environ)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
-    if path != "peer":
+    if path == "peer_unfused":
+        os.environ["QMM_PEER_FUSED"] = "0"
+    elif path != "peer":
         os.environ["QMM_ALLREDUCE"] = path
+    bit_exact = path in ("peer", "peer_unfused")
     try:
         procs = [ctx.Process(target=_rank_main, args=(r, world, port, shapes, c2p)) for r in range(world)]
         for p in procs:
             p.start()
         results = {}
-        for _ in range(world * (len(shapes) + 6)):
+        for _ in range(world * (len(shapes) + 7)):
             rank, key, y, q, s, digest = c2p.get(timeout=900)
             results[(rank, key)] = (y, q, s, digest)
         for p in procs:
@@ -205,7 +212,7 @@ def test_multi_rank(oracle, pkg, world, path):
             y = results[(r, key)][0].float().numpy()
             assert np.all(np.abs(y - total) <= 1e-2 * np.abs(total) + 1e-2 * mag), f"rank {r} shape {key}"
             assert np.array_equal(y, results[(0, key)][0].float().numpy())  # all ranks hold the same result
-        if path == "peer" and key[3] == 0:
+        if bit_exact and key[3] == 0:
             # the library's own kernel adds the ranks' rounded partials in fp32 in rank order and rounds once,
             # which is the oracle's order: bit-exact, not just within the tolerance
             assert torch.equal(results[(0, key)][0].view(torch.int16), rounded.view(torch.int16)), f"shape {key}"
@@ -222,8 +229,17 @@ def test_multi_rank(oracle, pkg, world, path):
         total, rounded = oracle.mm_all_reduce(q_list, w_list, scale, s_list, bias=bias, output_dtype=torch.bfloat16)
         for r in range(world):
             y = results[(r, key)][0]
-            if path == "peer":
+            if bit_exact:
                 assert torch.equal(y.view(torch.int16), rounded.view(torch.int16)), f"rank {r} chained call {i}"
             else:
                 assert np.all(np.abs(y.float().numpy() - total) <= 1e-2 * np.abs(total) + 2e-2 * np.abs(total).max())
             assert results[(r, key)][3] == results[(0, key)][3]
+    # which kernels did the exchange: the fused matmul for the prefill-sized shapes of the default path only
+    for r in range(world):
+        st = results[(r, ("stats",))][0]
+        if path == "peer":
+            assert st["peer_fused_calls"] >= 10 and st["nccl_calls"] >= 2, st
+        elif path == "nccl":
+            assert st["peer_calls"] == 0, st
+        else:
+            assert st["peer_fused_calls"] == 0 and st["peer_calls"] > 0, st

@@ -170,9 +170,9 @@ def _checksums(a_dev, w_dev, acc_dev):
     return np.array_equal(col.astype(np.float64), col_ref) and np.array_equal(row.astype(np.float64), row_ref)
 
 
-@pytest.mark.parametrize("KN", [(4096, 6144), (14336, 4096)])
+@pytest.mark.parametrize("KN", [(4096, 6144), (4096, 28672), (4096, 4096), (14336, 4096)])
 def test_prefill_full_size(capi, oracle, dev, KN):
-    """M = 8192 prefill GEMMs: oracle on a sample of rows, exact integer checksums over the whole result,
+    """The four M = 8192 prefill GEMMs of the 8B-class layer (QKV, gate/up, o_proj, down_proj): oracle on a sample of rows, exact integer checksums over the whole result,
     and the dequantized output of the sampled rows within 1 ulp."""
     K, N = KN
     M = 8192
