@@ -73,3 +73,61 @@ def test_row_parallel_allreduce_gloo_world2():
         p.join(timeout=120)
         assert p.exitcode == 0
     assert same and mag > 0
+
+
+def _mc2_rank_main(rank, world, port, q):
+    sys.path.insert(0, str(ROOT / "tests" / "golden"))
+    from make_mc2_golden import mc2_inputs
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rs_x1, rs_x2, ag_x1, ag_x2 = mc2_inputs(world)
+        # reduce-scatter matmul: own operands only, one collective, rank r keeps rows [r * M/W, (r+1) * M/W)
+        part = torch.matmul(rs_x1[rank].float(), rs_x2[rank].float())
+        dist.all_reduce(part, op=dist.ReduceOp.SUM)
+        rows = part.shape[0] // world
+        rs_out = part[rank * rows:(rank + 1) * rows].to(torch.float16)
+        # all-gather matmul: gather x1 in rank order, multiply by the rank's own x2
+        pieces = [torch.empty_like(ag_x1[rank]) for _ in range(world)]
+        dist.all_gather(pieces, ag_x1[rank])
+        gathered = torch.cat(pieces)
+        ag_out = torch.matmul(gathered.float(), ag_x2[rank].float()).to(torch.float16)
+        q.put((rank, rs_out, ag_out, gathered))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_mc2_contract_against_reference_golden_gloo_world2():
+    """Two gloo ranks carry out npu_mm_reduce_scatter_base and npu_all_gather_base_mm as distributed programs
+    (each rank touches its own operands only; which rows a rank keeps, and the order of the gathered rows, are the
+    operators' contract) and are compared with the outputs of the reference's own golden functions
+    (tests/golden/mc2_reference.npz), at the reference tests' tolerance."""
+    sys.path.insert(0, str(ROOT / "tests" / "golden"))
+    from make_mc2_golden import mc2_inputs
+
+    world = 2
+    golden = np.load(ROOT / "tests" / "golden" / "mc2_reference.npz")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 31500 + os.getpid() % 2000
+    procs = [ctx.Process(target=_mc2_rank_main, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = {}
+    for _ in range(world):
+        rank, rs_out, ag_out, gathered = q.get(timeout=120)
+        got[rank] = (rs_out, ag_out, gathered)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    ag_x1 = mc2_inputs(world)[2]
+    for r in range(world):
+        rs_ref = torch.from_numpy(golden["rs2_out"][r]).view(torch.float16)
+        ag_ref = torch.from_numpy(golden["ag2_out"][r]).view(torch.float16)
+        assert got[r][0].shape == rs_ref.shape and got[r][1].shape == ag_ref.shape
+        torch.testing.assert_close(got[r][0], rs_ref, rtol=1e-3, atol=1e-3)
+        torch.testing.assert_close(got[r][1], ag_ref, rtol=1e-3, atol=1e-3)
+        assert torch.equal(got[r][2], torch.cat(ag_x1))
