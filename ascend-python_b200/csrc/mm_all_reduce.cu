@@ -299,13 +299,17 @@ bool push_disabled() {
     return off;
 }
 
-// QMM_PEER_FUSED=0 keeps the reduce + gather in a kernel of its own behind the matmul.
-bool fused_disabled() {
-    static const bool off = [] {
+// Whether the matmul kernel also reduces and gathers (communication warps, peer_fused.cuh).  Measured on
+// B200s (M=4096, K=28672, N=8192, per call): 2 ranks 360 us fused against 383 us with the separate kernel;
+// 4 ranks 294-313 us against 261 us - with more ranks the 192 communication threads per SM move their share of
+// the exchange more slowly than a kernel that owns the whole GPU, and the tail outgrows what was hidden.  So the
+// default is fused for two ranks only; QMM_PEER_FUSED=1 forces it for any rank count, =0 switches it off.
+bool fused_wanted(int nranks) {
+    static const int mode = [] {
         const char *e = getenv("QMM_PEER_FUSED");
-        return e != nullptr && std::string(e) == "0";
+        return e == nullptr ? -1 : (std::string(e) == "0" ? 0 : 1);
     }();
-    return off;
+    return mode < 0 ? nranks == 2 : mode == 1;
 }
 
 // Column chunks of the fused kernel (QMM_PEER_FUSED_CHUNKS, 1..8): what is left to exchange when the matmul
@@ -534,7 +538,7 @@ extern "C" int qmm_mm_all_reduce(const int8_t *x1, int64_t ld_x1, const int8_t *
                 spec.rank = c.rank;
                 spec.rows_per = pp.rows_per;
                 opts.push = &spec;
-                if (pp.mc_base == nullptr && !fused_disabled()) {
+                if (pp.mc_base == nullptr && fused_wanted(c.nranks)) {
                     for (int r = 0; r < kPeerMaxRanks; ++r) fspec.base[r] = c.peer.base[r];
                     fspec.world = c.nranks;
                     fspec.rank = c.rank;
@@ -565,7 +569,6 @@ extern "C" int qmm_mm_all_reduce(const int8_t *x1, int64_t ld_x1, const int8_t *
                             QMM_CUDA_OK(cudaMemsetAsync(c.peer.base[c.rank] + kFusedFlagOffset + kFusedPushCountOffset, 0,
                                                         kFusedCounterBytes, s));
                     }
-                    fspec.debug = getenv("QMM_FUSED_DBG") ? atoi(getenv("QMM_FUSED_DBG")) : 0;
                     opts.fused = &fspec;
                 }
             }

@@ -12,9 +12,9 @@
 //      in rank order (fp32, one rounding: the result does not depend on timing and is the same on
 //      every rank), write them to the rank's output and to the reduced area of its region; the last
 //      CTA to finish raises reduced[c][rank] at every peer;
-//   3. one chunk later the communication warps copy the other owners' rows of chunk c from their
-//      regions into this rank's output (peer loads), each CTA from one owner, starting with the
-//      right-hand neighbour.
+//   3. then they copy the other owners' rows of chunk c from those owners' regions into this rank's
+//      output (peer loads), each CTA from one owner, starting with the right-hand neighbour; the owners
+//      reduce chunk c at the same time, so their flags follow shortly.
 //
 // The matmul roles never wait for the communication warps, and communication warps wait for flags
 // only, so there is no cycle: pushed[c] needs matmul progress alone, reduced[c] needs pushed[c].
@@ -49,6 +49,7 @@ struct FusedComm {
     int world, rank;
     uint32_t epoch;
     int chunks;                    // column chunks, 1..kFusedMaxChunks
+    int first[kFusedMaxChunks + 1];  // chunk c covers the tile columns [first[c], first[c + 1]); none is empty
     int64_t M, N;
     int64_t rows_per;              // rows owned by a rank, a multiple of 32
     size_t partial_off, red_off;   // byte offsets of the two data areas inside a region
@@ -56,12 +57,23 @@ struct FusedComm {
     uint32_t *status;
     uint32_t status_at_launch;
     int enabled;
-    int debug;                     // bit 0: communication warps do nothing (timing experiments only)
 };
 
-// first tile column of chunk c when `tiles_n` tile columns are cut into `chunks` chunks
-__device__ __host__ __forceinline__ int fused_chunk_first(int tiles_n, int chunks, int c) {
-    return static_cast<int>(static_cast<int64_t>(tiles_n) * c / chunks);
+// Cuts `tiles_n` tile columns into `chunks` (<= tiles_n) chunks whose widths fall off quadratically: what is
+// still to be exchanged when the matmul ends is the last chunk, so that one is the narrowest, while the wide
+// early chunks keep the number of flag rounds small.  No chunk is empty.
+inline void fused_chunk_bounds(int tiles_n, int chunks, int (&first)[kFusedMaxChunks + 1]) {
+    for (int c = 0; c <= kFusedMaxChunks; ++c) first[c] = tiles_n;
+    for (int c = 0; c <= chunks; ++c) {
+        const int64_t left = static_cast<int64_t>(chunks - c) * (chunks - c);
+        first[c] = tiles_n - static_cast<int>(tiles_n * left / (static_cast<int64_t>(chunks) * chunks));
+    }
+    for (int c = chunks - 1; c >= 1; --c)  // every chunk at least one column wide, from the back
+        if (first[c] > first[c + 1] - 1) first[c] = first[c + 1] - 1;
+    for (int c = 1; c <= chunks; ++c)
+        if (first[c] < first[c - 1] + 1) first[c] = first[c - 1] + 1;
+    first[0] = 0;
+    first[chunks] = tiles_n;
 }
 
 // Adds `add` to an arrival counter; true for the arrival that completes `expected`, which also puts the
@@ -141,7 +153,6 @@ __device__ __forceinline__ void fused_reduce_chunk(int W, int ct, uint32_t total
 template <typename T>
 __device__ __forceinline__ void fused_comm_role(const FusedComm &f, int ct, volatile uint32_t *s_ok) {
     const int W = f.world;
-    const int tiles_n = static_cast<int>((f.N + kFusedTileCols - 1) / kFusedTileCols);
     uint8_t *my_flags = f.base[f.rank] + kFusedFlagOffset;
     const uint32_t *pushed = reinterpret_cast<const uint32_t *>(my_flags);
     const uint32_t *reduced = reinterpret_cast<const uint32_t *>(my_flags + kFusedReducedOffset);
@@ -157,19 +168,18 @@ __device__ __forceinline__ void fused_comm_role(const FusedComm &f, int ct, vola
     const int64_t src_r0 = static_cast<int64_t>(gsrc) * f.rows_per;
     const int64_t src_r1 = (src_r0 + f.rows_per < f.M) ? src_r0 + f.rows_per : f.M;
     const int64_t src_rows = src_r1 > src_r0 ? src_r1 - src_r0 : 0;
-    if (f.debug & 1) return;
     if (ct == 0) *s_ok = 1;
     fused_bar_sync();
 
-    for (int c = 0; c <= f.chunks; ++c) {
-        if (c < f.chunks) {
+    for (int c = 0; c < f.chunks; ++c) {
+        {
             // ---- reduce chunk c of the rows this rank owns ----
             if (ct < W && !peer_wait_flag(pushed + c * kPeerMaxRanks + ct, f.epoch, f.status, f.status_at_launch, 0x11))
                 *s_ok = 0;
             fused_bar_sync();
             if (*s_ok == 0) return;
-            const int64_t col0 = static_cast<int64_t>(fused_chunk_first(tiles_n, f.chunks, c)) * kFusedTileCols;
-            int64_t col1 = static_cast<int64_t>(fused_chunk_first(tiles_n, f.chunks, c + 1)) * kFusedTileCols;
+            const int64_t col0 = static_cast<int64_t>(f.first[c]) * kFusedTileCols;
+            int64_t col1 = static_cast<int64_t>(f.first[c + 1]) * kFusedTileCols;
             if (col1 > f.N) col1 = f.N;
             const uint32_t vps = static_cast<uint32_t>((col1 - col0) / 8);  // 16-byte vectors per row segment
             const uint32_t total = static_cast<uint32_t>(own_rows) * vps;
@@ -196,17 +206,17 @@ __device__ __forceinline__ void fused_comm_role(const FusedComm &f, int ct, vola
                 }
             }
         }
-        if (c >= 1) {
-            // ---- gather chunk c-1 of one other owner's rows ----
-            const int g = c - 1;
+        {
+            // ---- gather chunk c of one other owner's rows (its reduce ran at the same time as this rank's) ----
+            const int g = c;
             // every CTA waits, also the ones without a slice: a rank may leave only after all peers are done reducing
             if (ct == 0 && !peer_wait_flag(reduced + g * kPeerMaxRanks + gsrc, f.epoch, f.status, f.status_at_launch, 0x12))
                 *s_ok = 0;
             fused_bar_sync();
             if (*s_ok == 0) return;
             if (gs < gn) {
-                const int64_t col0 = static_cast<int64_t>(fused_chunk_first(tiles_n, f.chunks, g)) * kFusedTileCols;
-                int64_t col1 = static_cast<int64_t>(fused_chunk_first(tiles_n, f.chunks, g + 1)) * kFusedTileCols;
+                const int64_t col0 = static_cast<int64_t>(f.first[g]) * kFusedTileCols;
+                int64_t col1 = static_cast<int64_t>(f.first[g + 1]) * kFusedTileCols;
                 if (col1 > f.N) col1 = f.N;
                 const uint32_t vps = static_cast<uint32_t>((col1 - col0) / 8);
                 const uint32_t total = static_cast<uint32_t>(src_rows) * vps;

@@ -86,12 +86,12 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tile
 // Tile order of the fused kernel: column chunk by column chunk; inside a chunk the order above (`raster`
 // chosen for a chunk's width), with the tile rows rotated by m_rot (the first tile row of the right-hand
 // neighbour's rows) so that the ranks do not all push to the same owner at the same time.
-__device__ __forceinline__ void fused_tile_coords(int tile, int tiles_m, int tiles_n, int chunks, int raster, int m_rot,
+__device__ __forceinline__ void fused_tile_coords(int tile, int tiles_m, const FusedComm &fc, int raster, int m_rot,
                                                   int &m_blk, int &n_blk, int &chunk) {
     int c = 0;
-    while (c + 1 < chunks && tile >= fused_chunk_first(tiles_n, chunks, c + 1) * tiles_m) ++c;
-    const int nb0 = fused_chunk_first(tiles_n, chunks, c);
-    const int ncols = fused_chunk_first(tiles_n, chunks, c + 1) - nb0;
+    while (c + 1 < fc.chunks && tile >= fc.first[c + 1] * tiles_m) ++c;
+    const int nb0 = fc.first[c];
+    const int ncols = fc.first[c + 1] - nb0;
     int m, n;
     pair_tile_coords(tile - nb0 * tiles_m, tiles_m, ncols, raster, m, n);
     n_blk = nb0 + n;
@@ -163,12 +163,12 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int pair_id = blockIdx.x >> 1;
     const int num_pairs = gridDim.x >> 1;
     // fused: first tile row of the right-hand neighbour's rows
-    const int m_rot = (FUSED && !(fc.debug & 2)) ? static_cast<int>((static_cast<int64_t>((fc.rank + 1) % fc.world) * fc.rows_per / (2 * kPM)) %
+    const int m_rot = FUSED ? static_cast<int>((static_cast<int64_t>((fc.rank + 1) % fc.world) * fc.rows_per / (2 * kPM)) %
                                                tiles_m)
                             : 0;
     auto tile_coords = [&](int tile, int &m_blk, int &n_blk, int &chunk) {
         if constexpr (FUSED) {
-            fused_tile_coords(tile, tiles_m, tiles_n, fc.chunks, raster, m_rot, m_blk, n_blk, chunk);
+            fused_tile_coords(tile, tiles_m, fc, raster, m_rot, m_blk, n_blk, chunk);
         } else {
             pair_tile_coords(tile, tiles_m, tiles_n, raster, m_blk, n_blk);
             chunk = 0;
@@ -294,15 +294,13 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         int cur_chunk = -1;
         uint32_t units = 0;
         auto chunk_expected = [&](int c) {
-            return static_cast<uint32_t>((fused_chunk_first(tiles_n, fc.chunks, c + 1) -
-                                          fused_chunk_first(tiles_n, fc.chunks, c)) * tiles_m * 2 * kPEpiWarps);
+            return static_cast<uint32_t>((fc.first[c + 1] - fc.first[c]) * tiles_m * 2 * kPEpiWarps);
         };
         for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++local) {
             int m_blk, n_blk, chunk;
             tile_coords(tile, m_blk, n_blk, chunk);
             if (FUSED && chunk != cur_chunk) {
-                if (cur_chunk >= 0 && lane == 0 && !(fc.debug & 4))
-                    fused_chunk_pushed(fc, cur_chunk, units, chunk_expected(cur_chunk));
+                if (cur_chunk >= 0 && lane == 0) fused_chunk_pushed(fc, cur_chunk, units, chunk_expected(cur_chunk));
                 cur_chunk = chunk;
                 units = 0;
             }
@@ -340,7 +338,7 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         if (lane == 0) tma_store_wait_all<0>();
         // a warp that was cut short reports nothing: the peers' bounded waits then run out
-        if (FUSED && ok && cur_chunk >= 0 && lane == 0 && !(fc.debug & 4)) fused_chunk_pushed(fc, cur_chunk, units, chunk_expected(cur_chunk));
+        if (FUSED && ok && cur_chunk >= 0 && lane == 0) fused_chunk_pushed(fc, cur_chunk, units, chunk_expected(cur_chunk));
         __syncwarp();
     }
 
@@ -436,8 +434,9 @@ int launch_pair_t(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_
             if (fc.chunks > kFusedMaxChunks) fc.chunks = kFusedMaxChunks;
             if (fc.chunks < 1) fc.chunks = 1;
             if (ep.M * ep.N < (1ll << 33)) {
-                // the order inside a chunk: as for a matmul of the chunk's width
-                const int64_t chunk_cols = static_cast<int64_t>((tiles_n + fc.chunks - 1) / fc.chunks) * kPN;
+                fused_chunk_bounds(tiles_n, fc.chunks, fc.first);
+                // the order inside a chunk: as for a matmul of the widest chunk's width
+                const int64_t chunk_cols = static_cast<int64_t>(fc.first[1]) * kPN;
                 raster = pair_choose_raster(ep.M, chunk_cols < ep.N ? chunk_cols : ep.N, K,
                                             static_cast<int64_t>(sizeof(OutT)), pairs_all);
                 fc.enabled = 1;

@@ -153,10 +153,10 @@ def _rank_main(rank, world, port, shapes, c2p):
 @pytest.mark.parametrize("world,path", [(2, "peer"), (2, "peer_unfused"), (2, "multimem"), (2, "nccl"), (4, "peer"),
                                         (4, "multimem"), (8, "peer"), (8, "peer_unfused"), (8, "multimem")])
 def test_multi_rank(oracle, pkg, world, path):
-    """path "peer": the default (calls with comm_turn == 0 reduce and gather through peer memory with plain peer
-    loads: inside the matmul kernel for prefill shapes, in a kernel of its own otherwise); "peer_unfused": always
-    in a kernel of its own; "multimem": the same with in-switch reduction / broadcast; "nccl" forces NCCL for
-    every call."""
+    """path "peer": calls with comm_turn == 0 reduce and gather through peer memory with plain peer loads inside
+    the matmul kernel for prefill shapes (the default for two ranks; forced here for any rank count), in a kernel
+    of its own otherwise; "peer_unfused": always in a kernel of its own; "multimem": the same with in-switch
+    reduction / broadcast; "nccl" forces NCCL for every call."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
@@ -174,7 +174,9 @@ def test_multi_rank(oracle, pkg, world, path):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     if path == "peer_unfused":
         os.environ["QMM_PEER_FUSED"] = "0"
-    elif path != "peer":
+    elif path == "peer":
+        os.environ["QMM_PEER_FUSED"] = "1"
+    else:
         os.environ["QMM_ALLREDUCE"] = path
     bit_exact = path in ("peer", "peer_unfused")
     try:
