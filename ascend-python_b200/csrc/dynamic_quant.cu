@@ -36,9 +36,10 @@ __global__ void __launch_bounds__(512)
 dynamic_quant_vec_kernel(const T *__restrict__ x, int64_t rows, int cols, int64_t ld_x, int8_t *__restrict__ q,
                          int64_t ld_q, float *__restrict__ scale, int tpr) {
     __shared__ float s_part[16];
-    const int rows_per_cta = blockDim.x / tpr;
-    const int row_in_cta = threadIdx.x / tpr;
-    const int t = threadIdx.x % tpr;
+    const int tpr_shift = __ffs(tpr) - 1;  // tpr is a power of two
+    const int rows_per_cta = blockDim.x >> tpr_shift;
+    const int row_in_cta = threadIdx.x >> tpr_shift;
+    const int t = threadIdx.x & (tpr - 1);
     const int64_t row = static_cast<int64_t>(blockIdx.x) * rows_per_cta + row_in_cta;
     const bool row_ok = row < rows;
     const int nvec = cols >> 3;
@@ -116,7 +117,9 @@ int launch_dynamic_quant(const T *x, int64_t rows, int64_t cols, int64_t ld_x, i
     if (vec_ok) {
         const int nvec = static_cast<int>(cols / 8);
         int tpr = 32;
-        while (tpr < 512 && tpr * 4 < nvec) tpr <<= 1;
+        // eight vectors per thread where the row is long enough: the kernels are bound by instruction issue, and
+        // the per-thread fixed cost (row scale, reductions, index arithmetic) is then spread over more elements
+        while (tpr < 512 && tpr * 8 < nvec) tpr <<= 1;
         const int need = (nvec + tpr - 1) / tpr;
         const int vpt = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
         const int threads = tpr > 256 ? tpr : 256;

@@ -8,13 +8,13 @@
 //      memory, slot [source rank] of the partial area).  An epilogue warp that leaves a chunk waits for
 //      its own stores to complete, and the last warp of the GPU to do so raises pushed[c][rank] at
 //      every rank;
-//   2. a rank's communication warps wait for pushed[c][*], add the W shares of the rows the rank owns
-//      in rank order (fp32, one rounding: the result does not depend on timing and is the same on
+//   2. five of a CTA's communication warps wait for pushed[c][*], add the W shares of the rows the rank
+//      owns in rank order (fp32, one rounding: the result does not depend on timing and is the same on
 //      every rank), write them to the rank's output and to the reduced area of its region; the last
 //      CTA to finish raises reduced[c][rank] at every peer;
-//   3. then they copy the other owners' rows of chunk c from those owners' regions into this rank's
-//      output (peer loads), each CTA from one owner, starting with the right-hand neighbour; the owners
-//      reduce chunk c at the same time, so their flags follow shortly.
+//   3. one thread of the sixth warp waits for reduced[c] of one other owner and copies that owner's rows
+//      of chunk c into this rank's output with bulk copies through two 16 KiB staging buffers (peer
+//      region -> shared memory -> output): the copy engine moves the data, no warp does.
 //
 // The matmul roles never wait for the communication warps, and communication warps wait for flags
 // only, so there is no cycle: pushed[c] needs matmul progress alone, reduced[c] needs pushed[c].
@@ -43,6 +43,8 @@ constexpr size_t kFusedPushCountOffset = 512;
 constexpr size_t kFusedReduceCountOffset = 576;
 constexpr size_t kFusedCounterBytes = 128;         // both counter rows
 constexpr int kFusedTileCols = 256;                // width of the matmul's output tile
+constexpr int kFusedReduceThreads = kFusedThreads - 32;  // five warps reduce, one drives the gather
+constexpr uint32_t kFusedStageBytes = 16 * 1024;   // one of the two staging buffers of the gather
 
 struct FusedComm {
     uint8_t *base[kPeerMaxRanks];  // every rank's region as mapped here (own region included)
@@ -87,7 +89,6 @@ __device__ __forceinline__ bool counter_arrive(uint32_t *ctr, uint32_t add, uint
     return true;
 }
 
-__device__ __forceinline__ void fused_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kFusedThreads) : "memory"); }
 
 // Called by an epilogue warp's lane 0 when the warp has issued the stores of `units` tiles of chunk c and
 // moves on: waits for the stores, counts them, and tells every rank once the whole GPU is done with c.
@@ -113,8 +114,8 @@ __device__ __forceinline__ void fused_reduce_chunk(int W, int ct, uint32_t total
                                                    size_t share_bytes, const uint8_t *part0, uint8_t *red0,
                                                    uint8_t *out0) {
     // 32-bit indices: a rank's rows of a chunk are far fewer than 2^31 vectors (checked by the launcher)
-    const uint32_t stride = gridDim.x * kFusedThreads;
-    for (uint32_t v = blockIdx.x * kFusedThreads + ct; v < total; v += U * stride) {
+    const uint32_t stride = gridDim.x * kFusedReduceThreads;
+    for (uint32_t v = blockIdx.x * kFusedReduceThreads + ct; v < total; v += U * stride) {
         uint4 part[U][WW];
         uint32_t off[U];  // a rank's share of the rows stays far below 4 GiB
 #pragma unroll
@@ -149,102 +150,150 @@ __device__ __forceinline__ void fused_reduce_chunk(int W, int ct, uint32_t total
     }
 }
 
-// The communication warps' loop; `ct` = 0..kFusedThreads-1, s_ok = a shared word of the CTA (set to 1 here).
+// Bulk copy shared -> global as a bulk group of the issuing thread (both addresses 16-byte aligned,
+// `bytes` a multiple of 16).
+__device__ __forceinline__ void bulk_store_1d(void *dst, uint32_t smem_src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(reinterpret_cast<uint64_t>(dst)),
+                 "r"(smem_src), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ void fused_reduce_bar_sync() {
+    asm volatile("bar.sync 1, %0;" ::"n"(kFusedReduceThreads) : "memory");
+}
+
+// The reduce warps' loop (communication warps 1..5); `rt` = 0..kFusedReduceThreads-1, s_ok = a shared word.
 template <typename T>
-__device__ __forceinline__ void fused_comm_role(const FusedComm &f, int ct, volatile uint32_t *s_ok) {
+__device__ __forceinline__ void fused_reduce_role(const FusedComm &f, int rt, volatile uint32_t *s_ok) {
     const int W = f.world;
     uint8_t *my_flags = f.base[f.rank] + kFusedFlagOffset;
     const uint32_t *pushed = reinterpret_cast<const uint32_t *>(my_flags);
-    const uint32_t *reduced = reinterpret_cast<const uint32_t *>(my_flags + kFusedReducedOffset);
     const int64_t own_r0 = static_cast<int64_t>(f.rank) * f.rows_per;
     const int64_t own_r1 = (own_r0 + f.rows_per < f.M) ? own_r0 + f.rows_per : f.M;
     const int64_t own_rows = own_r1 > own_r0 ? own_r1 - own_r0 : 0;
     const size_t row_bytes = static_cast<size_t>(f.N) * sizeof(T);
     const size_t share_bytes = static_cast<size_t>(f.rows_per) * row_bytes;
-    // gather: this CTA copies slice `gs` of `gn` from owner `gsrc`
+    if (rt == 0) *s_ok = 1;
+    fused_reduce_bar_sync();
+    for (int c = 0; c < f.chunks; ++c) {
+        if (rt < W && !peer_wait_flag(pushed + c * kPeerMaxRanks + rt, f.epoch, f.status, f.status_at_launch, 0x11))
+            *s_ok = 0;
+        fused_reduce_bar_sync();
+        if (*s_ok == 0) return;
+        const int64_t col0 = static_cast<int64_t>(f.first[c]) * kFusedTileCols;
+        int64_t col1 = static_cast<int64_t>(f.first[c + 1]) * kFusedTileCols;
+        if (col1 > f.N) col1 = f.N;
+        const uint32_t vps = static_cast<uint32_t>((col1 - col0) / 8);  // 16-byte vectors per row segment
+        const uint32_t total = static_cast<uint32_t>(own_rows) * vps;
+        const uint8_t *part0 = f.base[f.rank] + f.partial_off + static_cast<size_t>(col0) * sizeof(T);
+        const size_t own_byte0 = static_cast<size_t>(own_r0) * row_bytes + static_cast<size_t>(col0) * sizeof(T);
+        uint8_t *red0 = f.base[f.rank] + f.red_off + own_byte0;
+        uint8_t *out0 = static_cast<uint8_t *>(f.out) + own_byte0;
+        if (W <= 2)
+            fused_reduce_chunk<T, 2, 4>(W, rt, total, vps, row_bytes, share_bytes, part0, red0, out0);
+        else if (W <= 4)
+            fused_reduce_chunk<T, 4, 2>(W, rt, total, vps, row_bytes, share_bytes, part0, red0, out0);
+        else
+            fused_reduce_chunk<T, 8, 1>(W, rt, total, vps, row_bytes, share_bytes, part0, red0, out0);
+        fused_reduce_bar_sync();
+        if (rt == 0) {
+            __threadfence();
+            if (counter_arrive(reinterpret_cast<uint32_t *>(my_flags + kFusedReduceCountOffset) + c, 1, gridDim.x)) {
+                __threadfence_system();
+                for (int r = 0; r < W; ++r)
+                    if (r != f.rank)
+                        st_release_sys(reinterpret_cast<uint32_t *>(f.base[r] + kFusedFlagOffset + kFusedReducedOffset) +
+                                           c * kPeerMaxRanks + f.rank,
+                                       f.epoch);
+            }
+        }
+    }
+}
+
+// The gather, driven by ONE thread per CTA (lane 0 of communication warp 0) with bulk copies: the reduced rows
+// of one other owner travel peer region -> 16 KiB staging buffer in shared memory -> this rank's output,
+// two buffers in flight, so the copy engine moves the data and no warp spends registers or issue slots on
+// it.  `stage` = shared-memory address of the two staging buffers, `bar` = of their two mbarriers.
+template <typename T>
+__device__ __forceinline__ void fused_gather_role(const FusedComm &f, uint32_t stage, uint32_t bar,
+                                                  volatile uint32_t *abort_flag) {
+    const int W = f.world;
+    const uint32_t *reduced =
+        reinterpret_cast<const uint32_t *>(f.base[f.rank] + kFusedFlagOffset + kFusedReducedOffset);
+    const size_t row_bytes = static_cast<size_t>(f.N) * sizeof(T);
+    // this CTA copies row slice `gs` of `gn` of owner `gsrc` (consecutive CTAs read from different owners,
+    // every rank starting with its right-hand neighbour)
     const int gn = static_cast<int>(gridDim.x) / (W - 1);
     const int gs = static_cast<int>(blockIdx.x) / (W - 1);
     const int gsrc = (f.rank + 1 + static_cast<int>(blockIdx.x) % (W - 1)) % W;
     const int64_t src_r0 = static_cast<int64_t>(gsrc) * f.rows_per;
     const int64_t src_r1 = (src_r0 + f.rows_per < f.M) ? src_r0 + f.rows_per : f.M;
     const int64_t src_rows = src_r1 > src_r0 ? src_r1 - src_r0 : 0;
-    if (ct == 0) *s_ok = 1;
-    fused_bar_sync();
-
+    const int64_t row_lo = gs < gn ? src_rows * gs / gn : 0, row_hi = gs < gn ? src_rows * (gs + 1) / gn : 0;
+    uint32_t phase[2] = {0, 0};
     for (int c = 0; c < f.chunks; ++c) {
-        {
-            // ---- reduce chunk c of the rows this rank owns ----
-            if (ct < W && !peer_wait_flag(pushed + c * kPeerMaxRanks + ct, f.epoch, f.status, f.status_at_launch, 0x11))
-                *s_ok = 0;
-            fused_bar_sync();
-            if (*s_ok == 0) return;
-            const int64_t col0 = static_cast<int64_t>(f.first[c]) * kFusedTileCols;
-            int64_t col1 = static_cast<int64_t>(f.first[c + 1]) * kFusedTileCols;
-            if (col1 > f.N) col1 = f.N;
-            const uint32_t vps = static_cast<uint32_t>((col1 - col0) / 8);  // 16-byte vectors per row segment
-            const uint32_t total = static_cast<uint32_t>(own_rows) * vps;
-            const uint8_t *part0 = f.base[f.rank] + f.partial_off + static_cast<size_t>(col0) * sizeof(T);
-            const size_t own_byte0 = static_cast<size_t>(own_r0) * row_bytes + static_cast<size_t>(col0) * sizeof(T);
-            uint8_t *red0 = f.base[f.rank] + f.red_off + own_byte0;
-            uint8_t *out0 = static_cast<uint8_t *>(f.out) + own_byte0;
-            if (W <= 2)
-                fused_reduce_chunk<T, 2, 4>(W, ct, total, vps, row_bytes, share_bytes, part0, red0, out0);
-            else if (W <= 4)
-                fused_reduce_chunk<T, 4, 2>(W, ct, total, vps, row_bytes, share_bytes, part0, red0, out0);
-            else
-                fused_reduce_chunk<T, 8, 1>(W, ct, total, vps, row_bytes, share_bytes, part0, red0, out0);
-            fused_bar_sync();
-            if (ct == 0) {
-                __threadfence();
-                if (counter_arrive(reinterpret_cast<uint32_t *>(my_flags + kFusedReduceCountOffset) + c, 1, gridDim.x)) {
-                    __threadfence_system();
-                    for (int r = 0; r < W; ++r)
-                        if (r != f.rank)
-                            st_release_sys(reinterpret_cast<uint32_t *>(f.base[r] + kFusedFlagOffset + kFusedReducedOffset) +
-                                               c * kPeerMaxRanks + f.rank,
-                                           f.epoch);
+        // every CTA waits, also the ones without a slice: a rank may leave only after all peers are done reducing
+        if (!peer_wait_flag(reduced + c * kPeerMaxRanks + gsrc, f.epoch, f.status, f.status_at_launch, 0x12)) return;
+        const int64_t col0 = static_cast<int64_t>(f.first[c]) * kFusedTileCols;
+        int64_t col1 = static_cast<int64_t>(f.first[c + 1]) * kFusedTileCols;
+        if (col1 > f.N) col1 = f.N;
+        const uint32_t seg = static_cast<uint32_t>((col1 - col0) * sizeof(T));  // bytes of a row's share of the chunk
+        const uint32_t piece = seg <= kFusedStageBytes ? seg : 8192u;             // bytes per bulk copy
+        const uint32_t ppr = (seg + piece - 1) / piece;                           // pieces per row
+        const uint32_t per_batch = kFusedStageBytes / piece;                      // pieces per staging buffer
+        const size_t byte0 = static_cast<size_t>(src_r0) * row_bytes + static_cast<size_t>(col0) * sizeof(T);
+        const uint8_t *from = f.base[gsrc] + f.red_off + byte0;
+        uint8_t *to = static_cast<uint8_t *>(f.out) + byte0;
+        const uint32_t npieces = static_cast<uint32_t>(row_hi - row_lo) * ppr;
+        // batch j = pieces [j * per_batch, ...): load batch j + 1 while batch j lands, then store batch j
+        int prev_buf = -1;
+        uint32_t prev_first = 0, prev_count = 0;
+        int buf = 0;
+        for (uint32_t first = 0; first < npieces || prev_buf >= 0; first += per_batch) {
+            const uint32_t count = first < npieces ? (npieces - first < per_batch ? npieces - first : per_batch) : 0;
+            if (count > 0) {
+                // the bulk stores that last read this buffer (two batches ago) are all committed: wait for their reads
+                tma_store_wait_read<0>();
+                uint32_t bytes = 0;
+                for (uint32_t i = 0; i < count; ++i) {
+                    const uint32_t pi = first + i, off = (pi % ppr) * piece;
+                    bytes += (seg - off < piece) ? seg - off : piece;
+                }
+                mbar_expect_tx(bar + buf * 8, bytes);
+                uint32_t at = 0;
+                for (uint32_t i = 0; i < count; ++i) {
+                    const uint32_t pi = first + i, off = (pi % ppr) * piece;
+                    const uint32_t n = (seg - off < piece) ? seg - off : piece;
+                    bulk_load_1d(stage + buf * kFusedStageBytes + at,
+                                 from + static_cast<size_t>(row_lo + pi / ppr) * row_bytes + off, n, bar + buf * 8);
+                    at += n;
                 }
             }
-        }
-        {
-            // ---- gather chunk c of one other owner's rows (its reduce ran at the same time as this rank's) ----
-            const int g = c;
-            // every CTA waits, also the ones without a slice: a rank may leave only after all peers are done reducing
-            if (ct == 0 && !peer_wait_flag(reduced + g * kPeerMaxRanks + gsrc, f.epoch, f.status, f.status_at_launch, 0x12))
-                *s_ok = 0;
-            fused_bar_sync();
-            if (*s_ok == 0) return;
-            if (gs < gn) {
-                const int64_t col0 = static_cast<int64_t>(f.first[g]) * kFusedTileCols;
-                int64_t col1 = static_cast<int64_t>(f.first[g + 1]) * kFusedTileCols;
-                if (col1 > f.N) col1 = f.N;
-                const uint32_t vps = static_cast<uint32_t>((col1 - col0) / 8);
-                const uint32_t total = static_cast<uint32_t>(src_rows) * vps;
-                const uint32_t lo = static_cast<uint32_t>(static_cast<uint64_t>(total) * gs / gn);
-                const uint32_t hi = static_cast<uint32_t>(static_cast<uint64_t>(total) * (gs + 1) / gn);
-                const size_t src_byte0 = static_cast<size_t>(src_r0) * row_bytes + static_cast<size_t>(col0) * sizeof(T);
-                const uint8_t *from = f.base[gsrc] + f.red_off + src_byte0;
-                uint8_t *to = static_cast<uint8_t *>(f.out) + src_byte0;
-                for (uint32_t v0 = lo + ct; v0 < hi; v0 += 8 * kFusedThreads) {
-                    uint4 tmp[8];
-                    uint32_t off[8];
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        const uint32_t vv = v0 + u * kFusedThreads;
-                        if (vv < hi) {
-                            const uint32_t row = vv / vps;
-                            off[u] = static_cast<uint32_t>(static_cast<size_t>(row) * row_bytes +
-                                                           static_cast<size_t>(vv - row * vps) * 16);
-                            tmp[u] = __ldcg(reinterpret_cast<const uint4 *>(from + off[u]));
-                        }
-                    }
-#pragma unroll
-                    for (int u = 0; u < 8; ++u)
-                        if (v0 + u * kFusedThreads < hi) *reinterpret_cast<uint4 *>(to + off[u]) = tmp[u];
+            if (prev_buf >= 0) {
+                if (!mbar_wait(bar + prev_buf * 8, phase[prev_buf], abort_flag, 0x13)) return;
+                phase[prev_buf] ^= 1;
+                fence_proxy_async_smem();
+                uint32_t at = 0;
+                for (uint32_t i = 0; i < prev_count; ++i) {
+                    const uint32_t pi = prev_first + i, off = (pi % ppr) * piece;
+                    const uint32_t n = (seg - off < piece) ? seg - off : piece;
+                    bulk_store_1d(to + static_cast<size_t>(row_lo + pi / ppr) * row_bytes + off,
+                                  stage + prev_buf * kFusedStageBytes + at, n);
+                    at += n;
                 }
+                tma_store_commit();
+            }
+            if (count > 0) {
+                prev_buf = buf;
+                prev_first = first;
+                prev_count = count;
+                buf ^= 1;
+            } else {
+                prev_buf = -1;
             }
         }
     }
+    tma_store_wait_all<0>();
 }
 
 }  // namespace qmm

@@ -52,6 +52,7 @@ struct PairSmemTail {
     uint32_t tmem_base;
     uint32_t abort_flag;
     uint32_t comm_ok;
+    uint64_t comm_full[2];  // fused kernel: the gather's two staging buffers have landed
 };
 
 constexpr size_t kPairSmemBytes = kPStages * kPStageBytes + kPEpiWarps * kPEpiStageBytes +
@@ -162,6 +163,9 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int num_kb = (K + kPK - 1) / kPK;
     const int pair_id = blockIdx.x >> 1;
     const int num_pairs = gridDim.x >> 1;
+    // the fused kernel gives its last stage (32 KiB) to the gather's staging buffers
+    constexpr int kStages = FUSED ? kPStages - 1 : kPStages;
+    static_assert(2 * kFusedStageBytes <= kPStageBytes, "the gather's staging buffers take one stage");
     // fused: first tile row of the right-hand neighbour's rows
     const int m_rot = FUSED ? static_cast<int>((static_cast<int64_t>((fc.rank + 1) % fc.world) * fc.rows_per / (2 * kPM)) %
                                                tiles_m)
@@ -184,6 +188,8 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             mbar_init(smem_u32(&tail->tmem_full[b]), 1);
             mbar_init(smem_u32(&tail->tmem_empty[b]), 2 * kPEpiWarps);
         }
+        mbar_init(smem_u32(&tail->comm_full[0]), 1);
+        mbar_init(smem_u32(&tail->comm_full[1]), 1);
         tail->abort_flag = 0;
         mbar_fence_init();
     }
@@ -226,7 +232,7 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         tma_load_2d_pair(sb, &tmap_b, kb * kPK, n0, full_leader);  // [128 n-rows][128 k-bytes]
                 }
                 __syncwarp();
-                if (++stage == kPStages) {
+                if (++stage == kStages) {
                     stage = 0;
                     phase ^= 1;
                 }
@@ -269,7 +275,7 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         accumulate = 1;
                     }
                     tc_commit_pair_warp(empty0 + stage * 8, 0x3);
-                    if (++stage == kPStages) {
+                    if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1;
                     }
@@ -279,8 +285,16 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
     } else if (FUSED && warp >= kPThreads / 32) {
         // ---------------- communication warps (both CTAs; fused kernel only) ----------------
-        if constexpr (FUSED)
-            fused_comm_role<OutT>(fc, static_cast<int>(threadIdx.x) - kPThreads, &tail->comm_ok);
+        if constexpr (FUSED) {
+            if (warp == kPThreads / 32) {
+                if (lane == 0)
+                    fused_gather_role<OutT>(fc, smem_base + kStages * kPStageBytes, smem_u32(&tail->comm_full[0]),
+                                            abort_flag);
+                __syncwarp();
+            } else {
+                fused_reduce_role<OutT>(fc, static_cast<int>(threadIdx.x) - kPThreads - 32, &tail->comm_ok);
+            }
+        }
     } else {
         // ---------------- epilogue warps (both CTAs) ----------------
         const int quarter = warp & 3;
