@@ -547,6 +547,342 @@ size_t p_packed_bytes(int64_t N, int64_t K) {
     return static_cast<size_t>((N + kPTileN - 1) / kPTileN) * static_cast<size_t>(p_blocks_k(K)) * kPBlockBytes;
 }
 
+// ---- one to four tokens: integer dot products on the CUDA cores ------------------------------------------
+//
+// For a handful of tokens the tensor cores have nothing to add: a thread owns one output column, reads its
+// 64 bytes of a block straight from global memory (a warp's loads are 512 contiguous bytes), splits each
+// packed word into two words of four unsigned bytes - `w ^ 0x88888888` turns the two's complement nibbles into
+// w + 8, `& 0x0f0f0f0f` and `>> 4 & 0x0f0f0f0f` are bytes (k, k+4, k+1, k+5) and (k+2, k+6, k+3, k+7) of a
+// group of eight k - and multiplies them with dp4a by the activations, which a small kernel in front has
+// turned into two int8 digits of a block floating-point form, in that byte order: per token and block of
+// 128 k, with e the exponent of the block's absmax,
+//     X = rint(x * 2^(14 - e))  (|X| <= 2^14),   X = 128 * d1 + d2,  d1 in [-128, 127], d2 in [0, 127].
+// An activation within 2^-6 of its block's absmax is represented exactly (16-bit floats carry 8 or 11
+// significant bits); smaller ones are rounded to 2^-14 of the absmax, far below the 2^-9 / 2^-12 of the
+// output's own rounding.  Per block the exact integers D1 = sum u*d1 and D2 = sum u*d2 (u = w + 8) give
+//     y[m, n] += scale * esc[m] * (128 D1 + D2) + (offset*scale - 8 scale) * xs[m],
+// esc = 2^(e - 14), xs = esc * sum X; the weight itself is never rounded.  About 1.3 instructions per weight
+// for one token, 3.3 for four: below what the HBM stream leaves time for.  Work is cut into equal contiguous
+// runs of blocks, many CTAs per SM; a tile's partial sums go to per-CTA slots that the last arriver adds in
+// slot order, as in the tensor-core kernel.
+constexpr int kGvMaxM = 4;
+constexpr int kGvThreads = kPTileN;  // one output column per thread
+constexpr int kGvCtasPerSm = 6;       // resident CTAs per SM (80 registers per thread: three blocks of weights in flight)
+
+struct GvParams {
+    const uint8_t *packed;
+    const void *bias;
+    void *out;
+    int64_t ld_out;
+    int N, tiles_n, nblocks, max_slots;
+    int max_run;         // most blocks of one tile a CTA works on in a row (sizes the shared-memory copy of the digits)
+    const uint4 *xd;     // digits [nblocks][M][2][8 x 16 bytes], bytes in the order the split words have
+    const float *esc;    // [nblocks][M]
+    const float *xs;     // [nblocks][M]
+    float *slots;        // [tiles_n][max_slots][M][128]
+    uint32_t *counters;  // [tiles_n], zero between calls
+};
+
+__device__ __forceinline__ uint4 ldg_stream(const uint8_t *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+template <typename T, int M>
+__global__ void __launch_bounds__(kGvThreads, kGvCtasPerSm)
+w4a16_gemv_kernel(GvParams p) {
+    extern __shared__ uint4 gv_smem[];  // digits of a run of blocks [nb][M][2][8], then esc [nb][M], xs [nb][M]
+    __shared__ uint32_t s_is_last;
+    const int r = threadIdx.x;
+    const int64_t total = static_cast<int64_t>(p.tiles_n) * p.nblocks;
+    const int64_t G = gridDim.x;
+    const int64_t u_begin = total * blockIdx.x / G;
+    const int64_t u_end = total * (blockIdx.x + 1) / G;
+    const T *bias = static_cast<const T *>(p.bias);
+    T *out = static_cast<T *>(p.out);
+    bool waited = false;
+    int64_t u = u_begin;
+    while (u < u_end) {
+        const int tile = static_cast<int>(u / p.nblocks);
+        const int64_t tile_begin = static_cast<int64_t>(tile) * p.nblocks;
+        const int64_t tile_end = tile_begin + p.nblocks;
+        const int64_t seg_end = tile_end < u_end ? tile_end : u_end;
+        const bool whole = (u == tile_begin && seg_end == tile_end);
+        const int64_t n = static_cast<int64_t>(tile) * kPTileN + r;
+        const bool n_ok = n < p.N;
+        const int nb = static_cast<int>(seg_end - u), b_first = static_cast<int>(u - tile_begin);
+        // the first two blocks' weights are on their way before anything else happens
+        const uint8_t *blk = p.packed + u * kPBlockBytes;
+        uint4 wv[kPSubs], n1[kPSubs], n2[kPSubs];
+#pragma unroll
+        for (int s = 0; s < kPSubs; ++s) {
+            wv[s] = ldg_stream(blk + (s * kPTileN + r) * 16);
+            n1[s] = nb > 1 ? ldg_stream(blk + kPBlockBytes + (s * kPTileN + r) * 16) : make_uint4(0, 0, 0, 0);
+        }
+        T s_raw = *reinterpret_cast<const T *>(blk + kPWBytes + r * 2);
+        T t_raw = *reinterpret_cast<const T *>(blk + kPWBytes + kPTileN * 2 + r * 2);
+        // the digits come from the kernel launched just before this one (programmatic dependent launch: this
+        // kernel may start while that one still runs)
+        if (!waited) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            waited = true;
+        }
+        __syncthreads();  // the previous segment's digits are no longer read
+        {
+            const int nvec = nb * M * 16;
+            const uint4 *src = p.xd + static_cast<int64_t>(b_first) * M * 16;
+            for (int i = r; i < nvec; i += kGvThreads) gv_smem[i] = __ldg(src + i);
+            float *tab = reinterpret_cast<float *>(gv_smem + p.max_run * M * 16);
+            for (int i = r; i < nb * M; i += kGvThreads) {
+                tab[i] = __ldg(p.esc + b_first * M + i);
+                tab[p.max_run * M + i] = __ldg(p.xs + b_first * M + i);
+            }
+        }
+        __syncthreads();
+        const float *esc_s = reinterpret_cast<const float *>(gv_smem + p.max_run * M * 16);
+        const float *xs_s = esc_s + p.max_run * M;
+        float y[M];
+#pragma unroll
+        for (int m = 0; m < M; ++m) y[m] = 0.0f;
+        for (int lb = 0; lb < nb; ++lb, blk += kPBlockBytes) {
+            // the weights of the block after the next one are requested before this block is worked on
+            if (lb + 2 < nb) {
+#pragma unroll
+                for (int s = 0; s < kPSubs; ++s) n2[s] = ldg_stream(blk + 2 * kPBlockBytes + (s * kPTileN + r) * 16);
+            }
+            T s_next = s_raw, t_next = t_raw;
+            if (lb + 1 < nb) {
+                s_next = *reinterpret_cast<const T *>(blk + kPBlockBytes + kPWBytes + r * 2);
+                t_next = *reinterpret_cast<const T *>(blk + kPBlockBytes + kPWBytes + kPTileN * 2 + r * 2);
+            }
+            int d1[M], d2[M];
+#pragma unroll
+            for (int m = 0; m < M; ++m) d1[m] = d2[m] = 0;
+            const uint4 *xd = gv_smem + lb * M * 16;
+#pragma unroll
+            for (int s = 0; s < kPSubs; ++s) {
+                const uint32_t words[4] = {wv[s].x, wv[s].y, wv[s].z, wv[s].w};
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {  // words 2h and 2h + 1 of the sub-step share one 16-byte digit vector
+                    const uint32_t w0 = words[2 * h] ^ 0x88888888u, w1 = words[2 * h + 1] ^ 0x88888888u;
+                    const int a0 = static_cast<int>(w0 & 0x0f0f0f0fu), b0 = static_cast<int>((w0 >> 4) & 0x0f0f0f0fu);
+                    const int a1 = static_cast<int>(w1 & 0x0f0f0f0fu), b1 = static_cast<int>((w1 >> 4) & 0x0f0f0f0fu);
+#pragma unroll
+                    for (int m = 0; m < M; ++m) {
+                        const uint4 x1 = xd[(m * 2 + 0) * 8 + s * 2 + h];  // the same address in every lane: a broadcast
+                        const uint4 x2 = xd[(m * 2 + 1) * 8 + s * 2 + h];
+                        d1[m] = __dp4a(a0, static_cast<int>(x1.x), d1[m]);
+                        d1[m] = __dp4a(b0, static_cast<int>(x1.y), d1[m]);
+                        d1[m] = __dp4a(a1, static_cast<int>(x1.z), d1[m]);
+                        d1[m] = __dp4a(b1, static_cast<int>(x1.w), d1[m]);
+                        d2[m] = __dp4a(a0, static_cast<int>(x2.x), d2[m]);
+                        d2[m] = __dp4a(b0, static_cast<int>(x2.y), d2[m]);
+                        d2[m] = __dp4a(a1, static_cast<int>(x2.z), d2[m]);
+                        d2[m] = __dp4a(b1, static_cast<int>(x2.w), d2[m]);
+                    }
+                }
+            }
+            const float sc = to_float(s_raw), tc = to_float(t_raw) - 8.0f * sc;
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                const float v = fmaf(static_cast<float>(d1[m]), 128.0f, static_cast<float>(d2[m]));
+                y[m] = fmaf(sc * esc_s[lb * M + m], v, y[m]);
+                y[m] = fmaf(tc, xs_s[lb * M + m], y[m]);
+            }
+#pragma unroll
+            for (int s = 0; s < kPSubs; ++s) {
+                wv[s] = n1[s];
+                n1[s] = n2[s];
+            }
+            s_raw = s_next;
+            t_raw = t_next;
+        }
+        const float bv = (n_ok && bias != nullptr) ? to_float(bias[n]) : 0.0f;
+        if (whole) {
+            if (n_ok) {
+#pragma unroll
+                for (int m = 0; m < M; ++m) out[static_cast<int64_t>(m) * p.ld_out + n] = from_float<T>(y[m] + bv);
+            }
+        } else {
+            const int first_cta = p_cta_of_item(tile_begin, total, G);
+            const int last_cta = p_cta_of_item(tile_end - 1, total, G);
+            const int nslots = last_cta - first_cta + 1;
+            const int64_t slot_elems = static_cast<int64_t>(M) * kPTileN;
+            float *tile_slots = p.slots + static_cast<int64_t>(tile) * p.max_slots * slot_elems;
+            float *mine = tile_slots + (static_cast<int>(blockIdx.x) - first_cta) * slot_elems + r;
+#pragma unroll
+            for (int m = 0; m < M; ++m) __stcg(mine + m * kPTileN, y[m]);
+            __threadfence();
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                const uint32_t old = atomicAdd(p.counters + tile, 1u);
+                const bool is_last = (old + 1 == static_cast<uint32_t>(nslots));
+                if (is_last) p.counters[tile] = 0;
+                s_is_last = is_last ? 1u : 0u;
+                __threadfence();
+            }
+            __syncthreads();
+            if (s_is_last != 0 && n_ok) {
+                float v[M];
+#pragma unroll
+                for (int m = 0; m < M; ++m) v[m] = 0.0f;
+                for (int sl = 0; sl < nslots; ++sl) {
+#pragma unroll
+                    for (int m = 0; m < M; ++m) v[m] += __ldcg(tile_slots + sl * slot_elems + m * kPTileN + r);
+                }
+#pragma unroll
+                for (int m = 0; m < M; ++m) out[static_cast<int64_t>(m) * p.ld_out + n] = from_float<T>(v[m] + bv);
+            }
+        }
+        u = seg_end;
+    }
+}
+
+// activations -> two int8 digits per element; grid (blocks along K incl. padding, M), 128 threads = the block's k
+template <typename T>
+__global__ void __launch_bounds__(128)
+w4a16_gemv_digits_kernel(const T *__restrict__ x, int64_t ld_x, int M, int64_t K, int8_t *__restrict__ xd,
+                         float *__restrict__ esc, float *__restrict__ xs) {
+    __shared__ float s_max[4];
+    __shared__ int s_sum[4];
+    __shared__ int s_bad[4];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the matmul may start its weight loads
+    const int blk = blockIdx.x, m = blockIdx.y;
+    const int kl = threadIdx.x;
+    const int64_t k = static_cast<int64_t>(blk) * kPChunkK + kl;
+    const float v = k < K ? to_float(x[static_cast<int64_t>(m) * ld_x + k]) : 0.0f;
+    float a = fabsf(v);
+    const bool finite = a <= 3.0e38f;
+    if (!finite) a = 0.0f;
+    int bad = finite ? 0 : 1;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+        bad |= __shfl_xor_sync(0xffffffffu, bad, o);
+    }
+    if ((kl & 31) == 0) {
+        s_max[kl >> 5] = a;
+        s_bad[kl >> 5] = bad;
+    }
+    __syncthreads();
+    const float amax = fmaxf(fmaxf(s_max[0], s_max[1]), fmaxf(s_max[2], s_max[3]));
+    const bool any_bad = (s_bad[0] | s_bad[1] | s_bad[2] | s_bad[3]) != 0;
+    int X = 0;
+    float e_scale = 0.0f;
+    if (amax > 0.0f) {
+        // e = floor(log2(amax)) + 1, so that |x| < 2^e; X = rint(x * 2^(14 - e))
+        int e;
+        (void)frexpf(amax, &e);
+        e_scale = ldexpf(1.0f, e - 14);
+        float q = rintf(ldexpf(v, 14 - e));
+        q = fminf(fmaxf(q, -16384.0f), 16383.0f);
+        X = (q == q) ? static_cast<int>(q) : 0;
+    }
+    const int dig[2] = {X >> 7, X & 127};
+    // byte position inside the block's 128-byte record (see the kernel's header for the order)
+    const int s = kl >> 5, i = (kl >> 3) & 3, e8 = kl & 7;
+    const int pos = (e8 & 1) ? 4 + (e8 >> 1) : (e8 >> 1);           // nibble position of k in the packed word
+    const int byte = s * 32 + i * 8 + ((pos & 1) ? 4 : 0) + (pos >> 1);
+#pragma unroll
+    for (int d = 0; d < 2; ++d)
+        xd[((static_cast<int64_t>(blk) * M + m) * 2 + d) * 128 + byte] = static_cast<int8_t>(dig[d]);
+    int sum = X;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if ((kl & 31) == 0) s_sum[kl >> 5] = sum;
+    __syncthreads();
+    if (kl == 0) {
+        const int tot = s_sum[0] + s_sum[1] + s_sum[2] + s_sum[3];
+        // a block that holds a NaN or an infinity poisons the token's outputs, as the plain arithmetic would
+        esc[blk * M + m] = any_bad ? __int_as_float(0x7fc00000) : e_scale;
+        xs[blk * M + m] = e_scale * static_cast<float>(tot);  // |tot| < 2^21: exact
+    }
+}
+
+struct GvPlan {
+    int tiles_n, nblocks, grid, max_slots, max_run;
+    size_t slots_bytes, xd_bytes, tab_bytes;
+};
+
+size_t gv_align256(size_t v) { return (v + 255) / 256 * 256; }
+
+GvPlan gv_make_plan(int64_t M, int64_t N, int64_t K) {
+    GvPlan pl;
+    pl.tiles_n = static_cast<int>((N + kPTileN - 1) / kPTileN);
+    pl.nblocks = p_blocks_k(K);
+    const int64_t total = static_cast<int64_t>(pl.tiles_n) * pl.nblocks;
+    const int64_t cap = static_cast<int64_t>(sm_count()) * kGvCtasPerSm;
+    pl.grid = static_cast<int>(total < cap ? total : cap);
+    const int64_t ipc = total / pl.grid;  // blocks per CTA, rounded down (>= 1)
+    pl.max_slots = static_cast<int>((pl.nblocks + ipc - 1) / ipc + 1);
+    pl.max_run = static_cast<int>(ipc + 1 < pl.nblocks ? ipc + 1 : pl.nblocks);
+    pl.slots_bytes = gv_align256(static_cast<size_t>(pl.tiles_n) * pl.max_slots * M * kPTileN * sizeof(float));
+    pl.xd_bytes = gv_align256(static_cast<size_t>(pl.nblocks) * M * 256);
+    pl.tab_bytes = gv_align256(static_cast<size_t>(pl.nblocks) * M * sizeof(float));
+    return pl;
+}
+
+size_t gv_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+    const GvPlan pl = gv_make_plan(M, N, K);
+    return kPCounterBytes + pl.slots_bytes + pl.xd_bytes + 2 * pl.tab_bytes;
+}
+
+template <typename T>
+int launch_gemv_t(const uint8_t *packed, const void *x, int64_t ld_x, const void *bias, void *out, int64_t ld_out,
+                  int64_t M, int64_t N, int64_t K, void *workspace, cudaStream_t stream) {
+    const GvPlan pl = gv_make_plan(M, N, K);
+    uint8_t *ws = static_cast<uint8_t *>(workspace);
+    int8_t *xd = reinterpret_cast<int8_t *>(ws + kPCounterBytes + pl.slots_bytes);
+    float *esc = reinterpret_cast<float *>(ws + kPCounterBytes + pl.slots_bytes + pl.xd_bytes);
+    float *xs = reinterpret_cast<float *>(ws + kPCounterBytes + pl.slots_bytes + pl.xd_bytes + pl.tab_bytes);
+    w4a16_gemv_digits_kernel<T><<<dim3(static_cast<unsigned>(pl.nblocks), static_cast<unsigned>(M)), 128, 0, stream>>>(
+        static_cast<const T *>(x), ld_x, static_cast<int>(M), K, xd, esc, xs);
+    QMM_CUDA_OK(cudaGetLastError());
+    GvParams p;
+    p.packed = packed;
+    p.bias = bias;
+    p.out = out;
+    p.ld_out = ld_out;
+    p.N = static_cast<int>(N);
+    p.tiles_n = pl.tiles_n;
+    p.nblocks = pl.nblocks;
+    p.max_slots = pl.max_slots;
+    p.max_run = pl.max_run;
+    p.xd = reinterpret_cast<const uint4 *>(xd);
+    p.esc = esc;
+    p.xs = xs;
+    p.counters = reinterpret_cast<uint32_t *>(ws);
+    p.slots = reinterpret_cast<float *>(ws + kPCounterBytes);
+    // programmatic dependent launch: the kernel starts (and requests its first weights) while the digits
+    // kernel still runs, and waits for it (griddepcontrol.wait) before it reads the digits
+    const size_t smem = static_cast<size_t>(pl.max_run) * M * (256 + 8);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(pl.grid));
+    cfg.blockDim = dim3(kGvThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    auto launch = [&](auto kern) -> int {
+        if (smem > 48 * 1024)
+            QMM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        QMM_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p));
+        return QMM_OK;
+    };
+    switch (M) {
+        case 1: return launch(w4a16_gemv_kernel<T, 1>);
+        case 2: return launch(w4a16_gemv_kernel<T, 2>);
+        case 3: return launch(w4a16_gemv_kernel<T, 3>);
+        default: return launch(w4a16_gemv_kernel<T, 4>);
+    }
+}
+
 template <typename T>
 int launch_prepacked_t(const uint8_t *packed, const void *x, int64_t ld_x, const void *bias, void *out, int64_t ld_out,
                        int64_t M, int64_t N, int64_t K, void *workspace, cudaStream_t stream) {
@@ -642,7 +978,11 @@ extern "C" int qmm_weight_quant_batchmatmul_prepacked_workspace_size(int64_t M, 
     using namespace qmm;
     QMM_REQUIRE(bytes != nullptr, "qmm_weight_quant_batchmatmul_prepacked_workspace_size: bytes is NULL");
     QMM_REQUIRE(M >= 0 && N >= 0 && K >= 0, "qmm_weight_quant_batchmatmul_prepacked_workspace_size: negative argument");
-    *bytes = (M > 0 && p_shape_ok(N, K, K)) ? kPCounterBytes + p_make_plan(M, N, K).slots_bytes : 0;
+    *bytes = 0;
+    if (M > 0 && p_shape_ok(N, K, K)) {
+        *bytes = kPCounterBytes + p_make_plan(M, N, K).slots_bytes;
+        if (M <= kGvMaxM && gv_workspace_bytes(M, N, K) > *bytes) *bytes = gv_workspace_bytes(M, N, K);
+    }
     return QMM_OK;
 }
 
@@ -670,6 +1010,12 @@ extern "C" int qmm_weight_quant_batchmatmul_prepacked(const void *x, int x_dtype
         return fail(QMM_ERR_WORKSPACE,
                     "qmm_weight_quant_batchmatmul_prepacked: workspace missing, not 256-byte aligned or too small");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (M <= kGvMaxM)  // a handful of tokens: dp4a on the CUDA cores, at the speed of the weight stream
+        return (x_dtype == QMM_DTYPE_BF16)
+                   ? launch_gemv_t<__nv_bfloat16>(static_cast<const uint8_t *>(packed), x, ld_x, bias, out, ld_out, M, N, K,
+                                                  workspace, s)
+                   : launch_gemv_t<__half>(static_cast<const uint8_t *>(packed), x, ld_x, bias, out, ld_out, M, N, K,
+                                           workspace, s);
     const size_t elt = 2;
     for (int64_t m0 = 0; m0 < M; m0 += kPMaxM) {  // 64 token rows per launch (the accumulator's columns)
         const int64_t mc = (M - m0) < kPMaxM ? (M - m0) : kPMaxM;
