@@ -547,7 +547,7 @@ size_t p_packed_bytes(int64_t N, int64_t K) {
     return static_cast<size_t>((N + kPTileN - 1) / kPTileN) * static_cast<size_t>(p_blocks_k(K)) * kPBlockBytes;
 }
 
-// ---- one to four tokens: integer dot products on the CUDA cores ------------------------------------------
+// ---- one or two tokens: integer dot products on the CUDA cores --------------------------------------------
 //
 // For a handful of tokens the tensor cores have nothing to add: a thread owns one output column, reads its
 // 64 bytes of a block straight from global memory (a warp's loads are 512 contiguous bytes), splits each
@@ -562,12 +562,16 @@ size_t p_packed_bytes(int64_t N, int64_t K) {
 // output's own rounding.  Per block the exact integers D1 = sum u*d1 and D2 = sum u*d2 (u = w + 8) give
 //     y[m, n] += scale * esc[m] * (128 D1 + D2) + (offset*scale - 8 scale) * xs[m],
 // esc = 2^(e - 14), xs = esc * sum X; the weight itself is never rounded.  About 1.3 instructions per weight
-// for one token, 3.3 for four: below what the HBM stream leaves time for.  Work is cut into equal contiguous
+// for one token; every further token adds 64 dp4a and 32 broadcast loads of digits from shared memory per block
+// and thread, and the shared-memory pipe makes that 7-8 us per token, so beyond two tokens the tensor-core
+// kernels are faster (the kernel itself is written for up to four).  Making the digits inside this kernel (every
+// CTA for its own blocks) instead of in a kernel in front was measured slower: 30 us against 26 us for one token.
+// Work is cut into equal contiguous
 // runs of blocks, many CTAs per SM; a tile's partial sums go to per-CTA slots that the last arriver adds in
 // slot order, as in the tensor-core kernel.
-constexpr int kGvMaxM = 4;
+constexpr int kGvMaxM = 2;            // measured (K=8192, N=28672): 26 / 33 us for 1 / 2 tokens, 41 / 51 us for 3 / 4
 constexpr int kGvThreads = kPTileN;  // one output column per thread
-constexpr int kGvCtasPerSm = 6;       // resident CTAs per SM (80 registers per thread: three blocks of weights in flight)
+constexpr int kGvCtasPerSm = 5;       // resident CTAs per SM (three blocks of weights in flight per thread; best of 4..8)
 
 struct GvParams {
     const uint8_t *packed;

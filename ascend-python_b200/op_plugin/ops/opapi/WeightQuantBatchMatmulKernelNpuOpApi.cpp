@@ -185,8 +185,9 @@ at::Tensor npu_weight_quant_batchmatmul(const at::Tensor &x, const at::Tensor &w
     at::Tensor sc = antiquant_scale.contiguous();
     at::Tensor oc = offset_real.defined() ? offset_real.contiguous() : offset_real;
     at::Tensor bc = bias_real.defined() ? bias_real.contiguous() : bias_real;
-    // more than eight token rows: the tensor-memory kernel over the prepacked stream is the faster one
-    if (prepack_enabled() && M > 8 && K > 0) {
+    // one or two token rows (integer dot products at the speed of the weight stream) and more than eight (operand
+    // unpacked into tensor memory): the kernels over the prepacked stream are the faster ones
+    if (prepack_enabled() && (M <= 2 || M > 8) && K > 0) {
         at::Tensor packed = prepacked_weight(wc, sc, oc, group, N, K);
         if (packed.defined()) {
             size_t ws_size = 0;

@@ -107,9 +107,9 @@ def test_argument_checks(torch_npu, dev):
 
 
 def test_weight_quant_batchmatmul_prepack_cache(torch_npu, capi, oracle, dev):
-    """More than eight token rows: the operator prepacks the weight once (pointer-keyed cache) and runs the
-    kernel over the prepacked stream; an in-place update of the weight invalidates the entry; eight rows or
-    fewer keep the stock layout."""
+    """One or two token rows and more than eight: the operator prepacks the weight once (pointer-keyed cache) and
+    runs the kernels over the prepacked stream; an in-place update of the weight invalidates the entry; three to
+    eight rows keep the stock layout."""
     x, w, scale, offset = oracle.make_w4a16_inputs(16, 1024, 512, seed=9)
     _, w2, _, _ = oracle.make_w4a16_inputs(16, 1024, 512, seed=10)
     xd, wd, sd, od = x.to(dev), w.to(dev), scale.to(dev), offset.to(dev)
@@ -123,6 +123,9 @@ def test_weight_quant_batchmatmul_prepack_cache(torch_npu, capi, oracle, dev):
     assert torch.equal(y3, direct3) and not torch.equal(y3, y1)
     y_small = torch_npu.npu_weight_quant_batchmatmul(xd[:4], wd, sd, od, antiquant_group_size=128)
     assert torch.equal(y_small, capi.weight_quant_batchmatmul(xd[:4].contiguous(), wd, sd, od, group_size=128))
+    y_one = torch_npu.npu_weight_quant_batchmatmul(xd[:1], wd, sd, od, antiquant_group_size=128)
+    assert torch.equal(y_one, capi.weight_quant_batchmatmul_prepacked(
+        xd[:1].contiguous(), capi.w4a16_prepack(wd, sd, od, group_size=128), 512))
     # a group the prepacked format does not cover (64) stays on the stock path and stays correct
     x5, w5, s5, o5 = oracle.make_w4a16_inputs(16, 512, 256, seed=11, group=64)
     y5 = torch_npu.npu_weight_quant_batchmatmul(x5.to(dev), w5.to(dev), s5.to(dev), o5.to(dev), antiquant_group_size=64)

@@ -67,7 +67,7 @@ def test_prepack_refusals(capi, dev):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("shape", [(1, 256, 64, 128), (4, 256, 128, 128), (16, 1024, 512, 128), (64, 2048, 1024, 128),
+@pytest.mark.parametrize("shape", [(1, 256, 64, 128), (2, 384, 200, 128), (2, 8192, 1024, 256), (4, 256, 128, 128), (16, 1024, 512, 128), (64, 2048, 1024, 128),
                                    (130, 512, 256, 128), (8, 512, 256, 512), (33, 4096, 7168, 128),
                                    (5, 8192, 2048 + 32, 128), (64, 1024, 4096, 1024), (12, 256, 8, 256),
                                    (16, 2048, 1024 + 72, 128), (48, 1152, 640, 384)])
@@ -92,7 +92,7 @@ def test_bias_and_no_offset(capi, oracle, dev):
     _assert_close(y, y_ref, _rss(oracle, x, packed_w, scale, None, 128), torch.bfloat16)
 
 
-@pytest.mark.parametrize("M", [1, 16, 64])
+@pytest.mark.parametrize("M", [1, 2, 16, 64])
 def test_decode_full_size(capi, oracle, dev, M):
     """K = 8192, N = 28672, group 128: oracle on a sample of 8-column groups, linearity over the whole output
     (f(2x) == 2 f(x) exactly: scaling by two commutes with every rounding), and run-to-run identity."""
