@@ -46,6 +46,20 @@ constexpr int kFusedTileCols = 256;                // width of the matmul's outp
 constexpr int kFusedReduceThreads = kFusedThreads - 32;  // five warps reduce, one drives the gather
 constexpr uint32_t kFusedStageBytes = 16 * 1024;   // one of the two staging buffers of the gather
 
+// Development builds (-DQMM_FUSED_TRACE): CTA 0 records %globaltimer at the steps of the exchange into the flag
+// area of its rank's region (64-bit slots at 48 KiB: 0 start, 1+c epilogue left chunk c, 9+c pushed[c] seen,
+// 17+c reduce of c done, 25+c reduced[c] seen, 33+c gather of c done, 41 matmul end, 42 gather end).
+#ifdef QMM_FUSED_TRACE
+constexpr size_t kFusedTraceOffset = 48 * 1024;
+#define QMM_TRACE(f, idx)                                                                                  \
+    do {                                                                                                   \
+        if (blockIdx.x == 0)                                                                               \
+            reinterpret_cast<unsigned long long *>((f).base[(f).rank] + kFusedTraceOffset)[idx] = globaltimer_ns(); \
+    } while (0)
+#else
+#define QMM_TRACE(f, idx) do { } while (0)
+#endif
+
 struct FusedComm {
     uint8_t *base[kPeerMaxRanks];  // every rank's region as mapped here (own region included)
     int world, rank;
@@ -180,6 +194,7 @@ __device__ __forceinline__ void fused_reduce_role(const FusedComm &f, int rt, vo
             *s_ok = 0;
         fused_reduce_bar_sync();
         if (*s_ok == 0) return;
+        if (rt == 0) QMM_TRACE(f, 9 + c);
         const int64_t col0 = static_cast<int64_t>(f.first[c]) * kFusedTileCols;
         int64_t col1 = static_cast<int64_t>(f.first[c + 1]) * kFusedTileCols;
         if (col1 > f.N) col1 = f.N;
@@ -197,6 +212,7 @@ __device__ __forceinline__ void fused_reduce_role(const FusedComm &f, int rt, vo
             fused_reduce_chunk<T, 8, 1>(W, rt, total, vps, row_bytes, share_bytes, part0, red0, out0);
         fused_reduce_bar_sync();
         if (rt == 0) {
+            QMM_TRACE(f, 17 + c);
             __threadfence();
             if (counter_arrive(reinterpret_cast<uint32_t *>(my_flags + kFusedReduceCountOffset) + c, 1, gridDim.x)) {
                 __threadfence_system();
@@ -234,6 +250,7 @@ __device__ __forceinline__ void fused_gather_role(const FusedComm &f, uint32_t s
     for (int c = 0; c < f.chunks; ++c) {
         // every CTA waits, also the ones without a slice: a rank may leave only after all peers are done reducing
         if (!peer_wait_flag(reduced + c * kPeerMaxRanks + gsrc, f.epoch, f.status, f.status_at_launch, 0x12)) return;
+        QMM_TRACE(f, 25 + c);
         const int64_t col0 = static_cast<int64_t>(f.first[c]) * kFusedTileCols;
         int64_t col1 = static_cast<int64_t>(f.first[c + 1]) * kFusedTileCols;
         if (col1 > f.N) col1 = f.N;
@@ -292,8 +309,10 @@ __device__ __forceinline__ void fused_gather_role(const FusedComm &f, uint32_t s
                 prev_buf = -1;
             }
         }
+        QMM_TRACE(f, 33 + c);
     }
     tma_store_wait_all<0>();
+    QMM_TRACE(f, 42);
 }
 
 }  // namespace qmm

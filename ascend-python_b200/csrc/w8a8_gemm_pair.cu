@@ -315,6 +315,8 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             tile_coords(tile, m_blk, n_blk, chunk);
             if (FUSED && chunk != cur_chunk) {
                 if (cur_chunk >= 0 && lane == 0) fused_chunk_pushed(fc, cur_chunk, units, chunk_expected(cur_chunk));
+                if (FUSED && cur_chunk >= 0 && warp == 2 && lane == 0) QMM_TRACE(fc, 1 + cur_chunk);
+                if (FUSED && cur_chunk < 0 && warp == 2 && lane == 0) QMM_TRACE(fc, 0);
                 cur_chunk = chunk;
                 units = 0;
             }
@@ -353,6 +355,8 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (lane == 0) tma_store_wait_all<0>();
         // a warp that was cut short reports nothing: the peers' bounded waits then run out
         if (FUSED && ok && cur_chunk >= 0 && lane == 0) fused_chunk_pushed(fc, cur_chunk, units, chunk_expected(cur_chunk));
+        if (FUSED && cur_chunk >= 0 && warp == 2 && lane == 0) QMM_TRACE(fc, 1 + cur_chunk);
+        if (FUSED && warp == 2 && lane == 0) QMM_TRACE(fc, 41);
         __syncwarp();
     }
 
