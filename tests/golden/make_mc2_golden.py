@@ -9,7 +9,7 @@ uniform(-1, 1), [128, 512] @ [512, 256] and [16, 512] @ [512, 256], 8 ranks), pl
 The inputs are not stored: ``mc2_inputs`` regenerates them from the seed (the tests import it); the file
 holds the reference's outputs, in full for 2 and 4 ranks and as SHA-256 digests for 8.
 
-    python tests/golden/make_mc2_golden.py /root/reference
+    python tests/golden/make_mc2_golden.py <path of the reference tree>
 """
 import ast
 import sys
@@ -53,7 +53,9 @@ def digest(tensors) -> str:
 
 
 def main():
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference") / "test" / "test_custom_ops"
+    if len(sys.argv) < 2:
+        raise SystemExit(__doc__)
+    ref = Path(sys.argv[1]) / "test" / "test_custom_ops"
     rs = reference_method(ref / "test_mm_reduce_scatter_base.py", "_construct_excepted_result")
     ag = reference_method(ref / "test_all_gather_base_mm.py", "_construct_excepted_result")
     out = {}

@@ -6,7 +6,7 @@ test/test_custom_ops/test_npu_rms_norm.py:10-18).  The file imports torch_npu at
 installable here, so the method's source is taken out of the file with ``ast`` and executed unmodified
 with numpy alone.  Run in a container that has the reference tree:
 
-    python tests/golden/make_rms_norm_golden.py /root/reference
+    python tests/golden/make_rms_norm_golden.py <path of the reference tree>
 """
 import ast
 import sys
@@ -28,7 +28,9 @@ def reference_golden(ref_root: Path):
 
 
 def main():
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit(__doc__)
+    ref_root = Path(sys.argv[1])
     golden = reference_golden(ref_root)
     rng = np.random.default_rng(20240607)
     out = {}
