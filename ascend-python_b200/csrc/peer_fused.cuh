@@ -247,9 +247,10 @@ __device__ __forceinline__ void fused_gather_role(const FusedComm &f, uint32_t s
     const int64_t src_rows = src_r1 > src_r0 ? src_r1 - src_r0 : 0;
     const int64_t row_lo = gs < gn ? src_rows * gs / gn : 0, row_hi = gs < gn ? src_rows * (gs + 1) / gn : 0;
     uint32_t phase[2] = {0, 0};
-    for (int c = 0; c < f.chunks; ++c) {
+    bool gave_up = false;
+    for (int c = 0; c < f.chunks && !gave_up; ++c) {
         // every CTA waits, also the ones without a slice: a rank may leave only after all peers are done reducing
-        if (!peer_wait_flag(reduced + c * kPeerMaxRanks + gsrc, f.epoch, f.status, f.status_at_launch, 0x12)) return;
+        if (!peer_wait_flag(reduced + c * kPeerMaxRanks + gsrc, f.epoch, f.status, f.status_at_launch, 0x12)) break;
         QMM_TRACE(f, 25 + c);
         const int64_t col0 = static_cast<int64_t>(f.first[c]) * kFusedTileCols;
         int64_t col1 = static_cast<int64_t>(f.first[c + 1]) * kFusedTileCols;
@@ -266,7 +267,7 @@ __device__ __forceinline__ void fused_gather_role(const FusedComm &f, uint32_t s
         int prev_buf = -1;
         uint32_t prev_first = 0, prev_count = 0;
         int buf = 0;
-        for (uint32_t first = 0; first < npieces || prev_buf >= 0; first += per_batch) {
+        for (uint32_t first = 0; (first < npieces || prev_buf >= 0) && !gave_up; first += per_batch) {
             const uint32_t count = first < npieces ? (npieces - first < per_batch ? npieces - first : per_batch) : 0;
             if (count > 0) {
                 // the bulk stores that last read this buffer (two batches ago) are all committed: wait for their reads
@@ -287,7 +288,10 @@ __device__ __forceinline__ void fused_gather_role(const FusedComm &f, uint32_t s
                 }
             }
             if (prev_buf >= 0) {
-                if (!mbar_wait(bar + prev_buf * 8, phase[prev_buf], abort_flag, 0x13)) return;
+                if (!mbar_wait(bar + prev_buf * 8, phase[prev_buf], abort_flag, 0x13)) {
+                    gave_up = true;  // a load that has not landed after the wait limit: nothing more to copy
+                    break;
+                }
                 phase[prev_buf] ^= 1;
                 fence_proxy_async_smem();
                 uint32_t at = 0;
@@ -311,6 +315,7 @@ __device__ __forceinline__ void fused_gather_role(const FusedComm &f, uint32_t s
         }
         QMM_TRACE(f, 33 + c);
     }
+    // also on the way out after a wait that gave up: the bulk stores already issued read shared memory
     tma_store_wait_all<0>();
     QMM_TRACE(f, 42);
 }
