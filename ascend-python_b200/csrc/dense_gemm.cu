@@ -1,10 +1,13 @@
 // Dense bf16/f16 matmul, fp32 accumulation: the compute half of npu_mm_reduce_scatter_base and
 // npu_all_gather_base_mm (see dense_gemm.cuh).
 //
-// Same skeleton as the W8A8 tile kernel: warp 0 feeds a ring of [128 x 64] A and [64 x 128] B stages by
-// TMA (128-byte swizzle), warp 1 issues four tcgen05.mma.kind::f16 128 x 128 x 16 per stage into one of
-// two TMEM accumulators, four epilogue warps drain the other one.  B is taken as stored: a row-major
-// [K, N] matrix is the MMA's MN-major operand (two 64-column boxes per stage), the transposed view of a
+// Same skeleton as the W8A8 tile kernel: warp 0 feeds a ring of [128 x 64] A and [64 x 256] B stages by
+// TMA (128-byte swizzle), warp 1 issues four tcgen05.mma.kind::f16 128 x 256 x 16 per stage into one of
+// two TMEM accumulators, four epilogue warps drain the other one.  (256 columns per MMA: a 128 x 128 x 16
+// MMA reads 8 KiB of operands in the 64 clocks it occupies the pipe, all of an SM's shared-memory
+// bandwidth, and the pipe was measured half idle; 128 x 256 x 16 reads 12 KiB in 128 clocks.)  B is
+// taken as stored: a row-major
+// [K, N] matrix is the MMA's MN-major operand (four 64-column boxes per stage), the transposed view of a
 // row-major [N, K] its K-major operand.  The epilogue either casts (+ bias) into a local 16-bit output or
 // stores the raw fp32 accumulator rows straight into the peer region of the rank that will reduce them.
 #include "dense_gemm.cuh"
@@ -15,13 +18,14 @@ namespace qmm {
 
 namespace {
 
-constexpr int kDM = 128, kDN = 128, kDK = 64;        // tile; kDK 16-bit elements = one 128-byte swizzle row
-constexpr int kDStages = 6;
+constexpr int kDM = 128, kDN = 256, kDK = 64;        // tile; kDK 16-bit elements = one 128-byte swizzle row
+constexpr int kDStages = 4;
 constexpr int kDABytes = kDM * kDK * 2;              // 16 KiB
-constexpr int kDBBytes = kDN * kDK * 2;              // 16 KiB
+constexpr int kDBBytes = kDN * kDK * 2;              // 32 KiB
+constexpr int kDBBoxBytes = 64 * kDK * 2;            // one [64 k-rows][64 n] box of an MN-major B: 8 KiB
 constexpr int kDStageBytes = kDABytes + kDBBytes;
 constexpr int kDThreads = 192;
-constexpr uint32_t kDTmemCols = 256;                 // two accumulators of 128 columns
+constexpr uint32_t kDTmemCols = 512;                 // two accumulators of 256 columns
 
 struct DenseSmemTail {
     uint64_t full[kDStages];
@@ -137,11 +141,12 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     mbar_expect_tx(full, kDStageBytes);
                     tma_load_2d(sa, &tmap_a, kb * kDK, m_blk * kDM, full);  // [128 rows][64 k]
                     if (B_MN_MAJOR) {
-                        // two [64 k-rows][64 n] boxes side by side
-                        tma_load_2d(sb, &tmap_b, n_blk * kDN, kb * kDK, full);
-                        tma_load_2d(sb + kDBBytes / 2, &tmap_b, n_blk * kDN + 64, kb * kDK, full);
+                        // four [64 k-rows][64 n] boxes side by side
+#pragma unroll
+                        for (int bx = 0; bx < kDN / 64; ++bx)
+                            tma_load_2d(sb + bx * kDBBoxBytes, &tmap_b, n_blk * kDN + bx * 64, kb * kDK, full);
                     } else {
-                        tma_load_2d(sb, &tmap_b, kb * kDK, n_blk * kDN, full);  // [128 n-rows][64 k]
+                        tma_load_2d(sb, &tmap_b, kb * kDK, n_blk * kDN, full);  // [256 n-rows][64 k]
                     }
                 }
                 __syncwarp();
@@ -158,10 +163,10 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         constexpr uint32_t kDescHi = smem_desc_hi_sw128(1024);
         constexpr uint32_t kStageStep = kDStageBytes >> 4;
         // A and K-major B: 16 k = 32 bytes (+2) per MMA.  MN-major B: 16 k-rows of 128 bytes = 2048 bytes (+128)
-        // per MMA, the second 64-column box half a stage further (leading offset).
+        // per MMA, the next 64-column box 8 KiB further (leading offset).
         constexpr uint32_t kBStep = B_MN_MAJOR ? (2048u >> 4) : 2u;
         const uint32_t a_lo0 = smem_desc_lo(smem_base, 16);
-        const uint32_t b_lo0 = smem_desc_lo(smem_base + kDABytes, B_MN_MAJOR ? kDBBytes / 2 : 16);
+        const uint32_t b_lo0 = smem_desc_lo(smem_base + kDABytes, B_MN_MAJOR ? kDBBoxBytes : 16);
         uint32_t stage = 0, phase = 0;
         int local = 0;
         bool ok = true;
