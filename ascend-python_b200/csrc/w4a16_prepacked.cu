@@ -565,7 +565,8 @@ size_t p_packed_bytes(int64_t N, int64_t K) {
 // for one token; every further token adds 64 dp4a and 32 broadcast loads of digits from shared memory per block
 // and thread, and the shared-memory pipe makes that 7-8 us per token, so beyond two tokens the tensor-core
 // kernels are faster (the kernel itself is written for up to four).  Making the digits inside this kernel (every
-// CTA for its own blocks) instead of in a kernel in front was measured slower: 30 us against 26 us for one token.
+// CTA for its own blocks) instead of in a kernel in front was measured slower: 30 us against 26 us for one token;
+// so was pulling lines of later blocks into L2 with prefetch instructions (29.6 us).
 // Two mma.sync forms of the same idea (the split words as register operands of m16n8k32.s8 on these digits, or
 // pairs (k, k+1) as 16-bit operands of m16n8k16) were built and measured for 3..16 tokens: correct, but the legacy
 // MMA instructions cost 10-19 clocks each per SM on this part (41 / 63 us at 8 tokens, 63 / 116 us at 16), slower
