@@ -451,7 +451,7 @@ int launch_pair_t(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_
             if (fc.chunks > tiles_n) fc.chunks = tiles_n;
             if (fc.chunks > kFusedMaxChunks) fc.chunks = kFusedMaxChunks;
             if (fc.chunks < 1) fc.chunks = 1;
-            if (ep.M * ep.N < (1ll << 33)) {
+            if (fc.rows_per * ep.N * static_cast<int64_t>(sizeof(OutT)) < (1ll << 32)) {  // 32-bit offsets inside a share
                 fused_chunk_bounds(tiles_n, fc.chunks, fc.first);
                 // the order inside a chunk: as for a matmul of the widest chunk's width
                 const int64_t chunk_cols = static_cast<int64_t>(fc.first[1]) * kPN;
