@@ -283,9 +283,11 @@ QMM_API int qmm_comm_stats(const char *name, int64_t *peer_calls, int64_t *peer_
  * sees them, in rank order (its own included), plus - where the regions are bound to an NVLink
  * multicast object - the multicast address (else NULL).  qmm_comm_peer_memory_size gives the size an
  * allreduce of [M][N] 16-bit values needs.  While regions are attached and large enough, calls
- * with comm_turn == 0 reduce and gather through NVLink loads in one kernel per rank instead of
- * NCCL; the environment variable QMM_ALLREDUCE=nccl switches that off (set it on every rank or on
- * none).  The choice depends only on M, N, comm_turn and the attached size, which all ranks share; on
+ * with comm_turn == 0 reduce and gather over NVLink in the library's own kernels instead of NCCL
+ * (for prefill-sized M on two ranks inside the matmul kernel itself, otherwise in one more kernel per
+ * rank); the environment variable QMM_ALLREDUCE=nccl switches that off, QMM_PEER_FUSED=0|1 forces the
+ * exchange out of / into the matmul kernel (set them on every rank or on none).  The choice depends
+ * only on M, N, comm_turn, the rank count, the attached size and those variables, which all ranks share; on
  * that path `out` must be 16-byte aligned and the stream must not be capturing (both are errors, not a
  * switch to NCCL that the other ranks would not follow).  Calls of different shapes may follow one
  * another without synchronisation in between.  bytes == 0 detaches. */
