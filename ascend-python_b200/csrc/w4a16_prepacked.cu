@@ -562,9 +562,10 @@ size_t p_packed_bytes(int64_t N, int64_t K) {
 // output's own rounding.  Per block the exact integers D1 = sum u*d1 and D2 = sum u*d2 (u = w + 8) give
 //     y[m, n] += scale * esc[m] * (128 D1 + D2) + (offset*scale - 8 scale) * xs[m],
 // esc = 2^(e - 14), xs = esc * sum X; the weight itself is never rounded.  About 1.3 instructions per weight
-// for one token; every further token adds 64 dp4a and 32 broadcast loads of digits from shared memory per block
-// and thread, and the shared-memory pipe makes that 7-8 us per token, so beyond two tokens the tensor-core
-// kernels are faster (the kernel itself is written for up to four).  Making the digits inside this kernel (every
+// for one token; every further token adds 64 dp4a per block and thread, which at the rate dp4a issues here costs
+// 7-8 us per token, so beyond two tokens the tensor-core kernels are faster (the kernel itself is written for up
+// to four).  A form with four columns per lane, which needs a quarter of the broadcast loads of digits, was
+// measured slower still (37 us against 33 us at two tokens): the loads are not the limit.  Making the digits inside this kernel (every
 // CTA for its own blocks) instead of in a kernel in front was measured slower: 30 us against 26 us for one token;
 // so was pulling lines of later blocks into L2 with prefetch instructions (29.6 us).
 // Two mma.sync forms of the same idea (the split words as register operands of m16n8k32.s8 on these digits, or
