@@ -58,6 +58,17 @@ def test_validation_needs_no_gpu(capi):
     regions = (ctypes.c_void_p * 2)(None, None)
     rc = lib.qmm_comm_attach_peer_memory(b"no-such-comm", regions, None, 1 << 20)
     assert rc == 5 and b"not registered" in lib.qmm_last_error()
+    # the prepacked W4A16 format: 8704-byte blocks of 128 columns x 128 k, an even number of blocks along K
+    assert capi.w4a16_prepack_size(28672, 8192, 128) == 224 * 64 * 8704
+    assert capi.w4a16_prepack_size(200, 384, 128) == 2 * 4 * 8704       # 200 -> 2 column tiles, 3 -> 4 blocks
+    assert capi.w4a16_prepack_size(256, 256, 64) == 0                  # group below 128: not covered
+    sizes = []
+    for M in (1, 2, 16, 64):
+        assert lib.qmm_weight_quant_batchmatmul_prepacked_workspace_size(M, 28672, 8192, ctypes.byref(n)) == 0
+        assert n.value >= 65536 and n.value % 256 == 0
+        sizes.append(n.value)
+    assert sizes == sorted(sizes)
+    assert lib.qmm_weight_quant_batchmatmul_prepacked_workspace_size(0, 28672, 8192, ctypes.byref(n)) == 0 and n.value == 0
 
 
 def test_missing_library_fails_loudly(capi, monkeypatch):
