@@ -29,6 +29,49 @@ __device__ __forceinline__ int requant_one(int32_t acc, float sc, float pt, bool
     return max(-128, min(127, __float2int_rn(v)));
 }
 
+// Sixteen columns per thread (64 bytes of accumulators in flight per thread, one 16-byte store), one row per
+// blockIdx.y step: no index division, per-column constants as 16-byte loads.  Needs N % 16 == 0 and 16-byte
+// aligned rows of `out`; other shapes take requant_kernel below.
+__global__ void __launch_bounds__(256)
+requant_vec16_kernel(const int32_t *__restrict__ acc, int64_t M, int64_t N, const float *__restrict__ scale,
+                     int scale_scalar, const float *__restrict__ pertoken, const float *__restrict__ offset,
+                     int offset_scalar, int8_t *__restrict__ out, int64_t ld_out) {
+    const int64_t n = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 16;
+    if (n >= N) return;
+    const bool has_pt = pertoken != nullptr, has_off = offset != nullptr;
+    float sc[16], off[16];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const float4 s4 = scale_scalar ? make_float4(__ldg(scale), __ldg(scale), __ldg(scale), __ldg(scale))
+                                       : __ldg(reinterpret_cast<const float4 *>(scale + n) + q);
+        float4 o4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (has_off)
+            o4 = offset_scalar ? make_float4(__ldg(offset), __ldg(offset), __ldg(offset), __ldg(offset))
+                               : __ldg(reinterpret_cast<const float4 *>(offset + n) + q);
+        sc[4 * q] = s4.x, sc[4 * q + 1] = s4.y, sc[4 * q + 2] = s4.z, sc[4 * q + 3] = s4.w;
+        off[4 * q] = o4.x, off[4 * q + 1] = o4.y, off[4 * q + 2] = o4.z, off[4 * q + 3] = o4.w;
+    }
+    for (int64_t m = blockIdx.y; m < M; m += gridDim.y) {
+        const int4 *src = reinterpret_cast<const int4 *>(acc + m * N + n);
+        int4 a[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) a[q] = __ldcs(src + q);
+        const float pt = has_pt ? __ldg(pertoken + m) : 1.0f;
+        uint32_t w[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int32_t av[4] = {a[q].x, a[q].y, a[q].z, a[q].w};
+            uint32_t packed = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                packed |= (static_cast<uint32_t>(requant_one(av[j], sc[4 * q + j], pt, has_pt, off[4 * q + j], has_off)) & 0xffu)
+                          << (8 * j);
+            w[q] = packed;
+        }
+        *reinterpret_cast<uint4 *>(out + m * ld_out + n) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
 // four columns per thread where N allows
 __global__ void __launch_bounds__(256)
 requant_kernel(const int32_t *__restrict__ acc, int64_t M, int64_t N, const float *__restrict__ scale, int scale_scalar,
@@ -109,6 +152,20 @@ extern "C" int qmm_quant_matmul_int8(const int8_t *x1, int64_t ld_x1, const int8
                               bias ? QMM_DTYPE_I32 : QMM_DTYPE_NONE, acc, QMM_DTYPE_I32, N, M, N, K, QMM_ALGO_AUTO,
                               inner ? workspace : nullptr, inner, stream);
     if (rc != QMM_OK) return rc;
+    const int scale_scalar = (scale_len == 1 && N != 1) ? 1 : 0, offset_scalar = (offset_len == 1 && N != 1) ? 1 : 0;
+    if ((N & 15) == 0 && (ld_out & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
+        (scale_scalar || (reinterpret_cast<uintptr_t>(scale) & 15) == 0) &&
+        (offset == nullptr || offset_scalar || (reinterpret_cast<uintptr_t>(offset) & 15) == 0)) {
+        const unsigned gx = static_cast<unsigned>((N / 16 + 255) / 256);
+        int64_t gy = static_cast<int64_t>(sm_count()) * 16 / gx;
+        if (gy > M) gy = M;
+        if (gy > 65535) gy = 65535;
+        if (gy < 1) gy = 1;
+        requant_vec16_kernel<<<dim3(gx, static_cast<unsigned>(gy)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            acc, M, N, scale, scale_scalar, pertoken_scale, offset, offset_scalar, out, ld_out);
+        QMM_CUDA_OK(cudaGetLastError());
+        return QMM_OK;
+    }
     const int64_t items = ((N & 3) == 0) ? M * (N >> 2) : M * N;
     int64_t grid = (items + 255) / 256;
     const int64_t cap = static_cast<int64_t>(sm_count()) * 16;

@@ -802,6 +802,18 @@ def run_case(args):
         xs = [torch.randn((M, K), device=dev, dtype=torch.bfloat16) for _ in range(nb)]
         gamma = torch.randn(K, device=dev, dtype=torch.bfloat16)
         fn = lambda i: capi.rms_norm_dynamic_quant(xs[i % nb], gamma, 1e-6)  # noqa: E731
+    elif args.case == "rms_norm":
+        xs = [torch.randn((M, K), device=dev, dtype=torch.bfloat16) for _ in range(nb)]
+        gamma = torch.randn(K, device=dev, dtype=torch.bfloat16)
+        fn = lambda i: capi.rms_norm(xs[i % nb], gamma, 1e-6)  # noqa: E731
+    elif args.case == "quant_matmul_int8":
+        # the requantized int8 output: int32 accumulator pass + requantize kernel
+        a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev)
+        ws = [torch.randint(-127, 128, (K, N), dtype=torch.int8, device=dev) for _ in range(nb)]
+        scale = torch.empty(N, device=dev).uniform_(1e-5, 1e-4)
+        offset = torch.empty(N, device=dev).uniform_(-4, 4)
+        pt = torch.empty(M, device=dev).uniform_(0.5, 2.0)
+        fn = lambda i: capi.quant_matmul_int8(a, ws[i % nb], scale, offset=offset, pertoken_scale=pt)  # noqa: E731
     else:
         x = torch.randn((M, K), device=dev, dtype=torch.bfloat16)
         packs = [torch.randint(-2 ** 31, 2 ** 31 - 1, (K, N // 8), device=dev, dtype=torch.int64).to(torch.int32)
@@ -832,7 +844,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--case", default=None, choices=["quant_matmul", "dynamic_quant", "w4a16", "w4a16_prepacked",
-                                                     "rms_norm_quant", "dense_matmul"],
+                                                     "rms_norm_quant", "dense_matmul", "rms_norm", "quant_matmul_int8"],
                     help="run one kernel a few times (profiling target) instead of the benchmark")
     ap.add_argument("--M", type=int, default=8192)
     ap.add_argument("--K", type=int, default=4096)
