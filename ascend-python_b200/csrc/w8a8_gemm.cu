@@ -369,6 +369,48 @@ int launch_tile(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_t x2_sk
 
 // Adds the slices' int32 sums, applies the epilogue and zeroes what it read (the scratch is shared with
 // the stream-K kernel, which relies on finding zeros).
+// Eight columns per thread, one row per blockIdx.y step: the slices' loads of a thread are all in flight at once,
+// the per-column constants are loaded once per thread and the 16-bit results leave as one 16-byte store.
+// Needs N % 8 == 0, a 16-bit output with 16-byte aligned rows, fp32 per-column scale and no int32 output.
+template <typename OutT, int SLICES>
+__global__ void __launch_bounds__(256)
+splitk_reduce_vec8_kernel(int32_t *__restrict__ scratch, int64_t slice_elems, EpilogueParams ep) {
+    const int64_t n = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
+    if (n >= ep.N) return;
+    const bool has_pt = ep.pertoken_scale != nullptr;
+    const bool has_bias = ep.bias != nullptr && ep.bias_dtype != QMM_DTYPE_NONE && ep.bias_dtype != QMM_DTYPE_I32;
+    float sc[8], bi[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        sc[j] = ep.scale_is_scalar ? __ldg(ep.scale) : __ldg(ep.scale + n + j);
+        bi[j] = has_bias ? load_bias_f32(ep, n + j) : 0.0f;
+    }
+    for (int64_t m = blockIdx.y; m < ep.M; m += gridDim.y) {
+        int4 a[SLICES][2];
+#pragma unroll
+        for (int s = 0; s < SLICES; ++s) {
+            int4 *src = reinterpret_cast<int4 *>(scratch + s * slice_elems + m * ep.N + n);
+            a[s][0] = __ldcg(src);
+            a[s][1] = __ldcg(src + 1);
+        }
+        int32_t acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+        for (int s = 0; s < SLICES; ++s) {
+            acc[0] += a[s][0].x, acc[1] += a[s][0].y, acc[2] += a[s][0].z, acc[3] += a[s][0].w;
+            acc[4] += a[s][1].x, acc[5] += a[s][1].y, acc[6] += a[s][1].z, acc[7] += a[s][1].w;
+            int4 *src = reinterpret_cast<int4 *>(scratch + s * slice_elems + m * ep.N + n);
+            __stcg(src, make_int4(0, 0, 0, 0));
+            __stcg(src + 1, make_int4(0, 0, 0, 0));
+        }
+        const float pt = has_pt ? __ldg(ep.pertoken_scale + m) : 1.0f;
+        float f[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = dequant_one(acc[j], sc[j], pt, has_pt, bi[j], has_bias);
+        *reinterpret_cast<uint4 *>(static_cast<OutT *>(ep.out) + m * ep.ld_out + n) =
+            make_uint4(pack2<OutT>(f[0], f[1]), pack2<OutT>(f[2], f[3]), pack2<OutT>(f[4], f[5]), pack2<OutT>(f[6], f[7]));
+    }
+}
+
 template <typename OutT>
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(int32_t *__restrict__ scratch, int slices, int64_t slice_elems, EpilogueParams ep) {
@@ -452,6 +494,28 @@ int launch_tile_splitk(const int8_t *x1, int64_t ld_x1, const int8_t *x2, int64_
     kern<<<grid, kTileThreads, kTileSmemBytes, stream>>>(ta, tb, tout, raw, static_cast<int>(K), 1, slices,
                                                          static_cast<int>(slice_rows), device_status_word());
     QMM_CUDA_OK(cudaGetLastError());
+    if constexpr (sizeof(OutT) == 2) {
+        if ((ep.N & 7) == 0 && (ep.ld_out & 7) == 0 && (reinterpret_cast<uintptr_t>(ep.out) & 15) == 0 && slices <= 8) {
+            const unsigned gx = static_cast<unsigned>((ep.N / 8 + 255) / 256);
+            int64_t gy = static_cast<int64_t>(sm_count()) * 8 / gx;
+            if (gy > ep.M) gy = ep.M;
+            if (gy < 1) gy = 1;
+            const dim3 rg(gx, static_cast<unsigned>(gy));
+            int32_t *sp = static_cast<int32_t *>(workspace);
+            const int64_t se = slice_rows * ep.N;
+            switch (slices) {
+                case 2: splitk_reduce_vec8_kernel<OutT, 2><<<rg, 256, 0, stream>>>(sp, se, ep); break;
+                case 3: splitk_reduce_vec8_kernel<OutT, 3><<<rg, 256, 0, stream>>>(sp, se, ep); break;
+                case 4: splitk_reduce_vec8_kernel<OutT, 4><<<rg, 256, 0, stream>>>(sp, se, ep); break;
+                case 5: splitk_reduce_vec8_kernel<OutT, 5><<<rg, 256, 0, stream>>>(sp, se, ep); break;
+                case 6: splitk_reduce_vec8_kernel<OutT, 6><<<rg, 256, 0, stream>>>(sp, se, ep); break;
+                case 7: splitk_reduce_vec8_kernel<OutT, 7><<<rg, 256, 0, stream>>>(sp, se, ep); break;
+                default: splitk_reduce_vec8_kernel<OutT, 8><<<rg, 256, 0, stream>>>(sp, se, ep); break;
+            }
+            QMM_CUDA_OK(cudaGetLastError());
+            return QMM_OK;
+        }
+    }
     const int64_t vecs = ep.M * ep.N / 4;
     const int rgrid = static_cast<int>(vecs / 256 + 1 < 4 * sm_count() ? vecs / 256 + 1 : 4 * sm_count());
     splitk_reduce_kernel<OutT><<<rgrid, 256, 0, stream>>>(static_cast<int32_t *>(workspace), slices,
