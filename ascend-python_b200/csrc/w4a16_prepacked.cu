@@ -750,64 +750,80 @@ w4a16_gemv_kernel(GvParams p) {
     }
 }
 
-// activations -> two int8 digits per element; grid (blocks along K incl. padding, M), 128 threads = the block's k
+// activations -> two int8 digits per element.  One warp per (block of 128 k, token): a lane takes four consecutive
+// k (one 8-byte load), the block's absmax and sum are warp shuffles, no shared memory and no CTA barrier; the
+// kernel is a few microseconds of latency in front of the matmul, so every step of it counts.
+// grid (ceil(blocks / 4), M), 128 threads.
 template <typename T>
 __global__ void __launch_bounds__(128)
-w4a16_gemv_digits_kernel(const T *__restrict__ x, int64_t ld_x, int M, int64_t K, int8_t *__restrict__ xd,
+w4a16_gemv_digits_kernel(const T *__restrict__ x, int64_t ld_x, int M, int64_t K, int nblocks, int8_t *__restrict__ xd,
                          float *__restrict__ esc, float *__restrict__ xs) {
-    __shared__ float s_max[4];
-    __shared__ int s_sum[4];
-    __shared__ int s_bad[4];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the matmul may start its weight loads
-    const int blk = blockIdx.x, m = blockIdx.y;
-    const int kl = threadIdx.x;
-    const int64_t k = static_cast<int64_t>(blk) * kPChunkK + kl;
-    const float v = k < K ? to_float(x[static_cast<int64_t>(m) * ld_x + k]) : 0.0f;
-    float a = fabsf(v);
-    const bool finite = a <= 3.0e38f;
-    if (!finite) a = 0.0f;
-    int bad = finite ? 0 : 1;
+    const int lane = threadIdx.x & 31;
+    const int blk = blockIdx.x * 4 + (threadIdx.x >> 5), m = blockIdx.y;
+    if (blk >= nblocks) return;
+    const int64_t k0 = static_cast<int64_t>(blk) * kPChunkK + lane * 4;
+    float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (k0 < K) {  // K is a multiple of 128: a block is inside or a padding block
+        const uint2 raw = __ldg(reinterpret_cast<const uint2 *>(x + static_cast<int64_t>(m) * ld_x + k0));
+        const T *h = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = to_float(h[j]);
+    }
+    float a = 0.0f;
+    int bad = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float av = fabsf(v[j]);
+        if (av <= 3.0e38f) a = fmaxf(a, av); else bad = 1;
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
         bad |= __shfl_xor_sync(0xffffffffu, bad, o);
     }
-    if ((kl & 31) == 0) {
-        s_max[kl >> 5] = a;
-        s_bad[kl >> 5] = bad;
-    }
-    __syncthreads();
-    const float amax = fmaxf(fmaxf(s_max[0], s_max[1]), fmaxf(s_max[2], s_max[3]));
-    const bool any_bad = (s_bad[0] | s_bad[1] | s_bad[2] | s_bad[3]) != 0;
-    int X = 0;
+    int e = 0, sum = 0;
     float e_scale = 0.0f;
-    if (amax > 0.0f) {
-        // e = floor(log2(amax)) + 1, so that |x| < 2^e; X = rint(x * 2^(14 - e))
-        int e;
-        (void)frexpf(amax, &e);
+    if (a > 0.0f) {
+        (void)frexpf(a, &e);  // a = f * 2^e, f in [0.5, 1): |x| < 2^e; X = rint(x * 2^(14 - e))
         e_scale = ldexpf(1.0f, e - 14);
-        float q = rintf(ldexpf(v, 14 - e));
-        q = fminf(fmaxf(q, -16384.0f), 16383.0f);
-        X = (q == q) ? static_cast<int>(q) : 0;
     }
-    const int dig[2] = {X >> 7, X & 127};
-    // byte position inside the block's 128-byte record (see the kernel's header for the order)
-    const int s = kl >> 5, i = (kl >> 3) & 3, e8 = kl & 7;
-    const int pos = (e8 & 1) ? 4 + (e8 >> 1) : (e8 >> 1);           // nibble position of k in the packed word
-    const int byte = s * 32 + i * 8 + ((pos & 1) ? 4 : 0) + (pos >> 1);
+    // byte positions inside the block's two 128-byte records (see the kernel's header for the order): the four k
+    // of a lane lie in one group of eight, whose two words are bytes [8 g, 8 g + 8) of the sub-step's 32
+    int8_t *rec = xd + (static_cast<int64_t>(blk) * M + m) * 256;
+    const int s = lane >> 3, i = (lane >> 1) & 3;
+    uint32_t d1w[2] = {0, 0}, d2w[2] = {0, 0};  // this lane's bytes of word A ([0]) and word B ([1]) of its group
 #pragma unroll
-    for (int d = 0; d < 2; ++d)
-        xd[((static_cast<int64_t>(blk) * M + m) * 2 + d) * 128 + byte] = static_cast<int8_t>(dig[d]);
-    int sum = X;
+    for (int j = 0; j < 4; ++j) {
+        int X = 0;
+        if (a > 0.0f) {
+            float q = rintf(ldexpf(v[j], 14 - e));
+            q = fminf(fmaxf(q, -16384.0f), 16383.0f);
+            X = (q == q) ? static_cast<int>(q) : 0;
+        }
+        sum += X;
+        const int e8 = (lane & 1) * 4 + j;                     // k within its group of eight
+        const int pos = (e8 & 1) ? 4 + (e8 >> 1) : (e8 >> 1);  // nibble position of that k in the packed word
+        const int word = pos & 1, byte = pos >> 1;
+        d1w[word] |= (static_cast<uint32_t>(X >> 7) & 0xffu) << (8 * byte);
+        d2w[word] |= (static_cast<uint32_t>(X & 127)) << (8 * byte);
+    }
+    // the two lanes of a group hold disjoint bytes of the same two words: merge them and let the even lane store
+#pragma unroll
+    for (int w = 0; w < 2; ++w) {
+        d1w[w] |= __shfl_xor_sync(0xffffffffu, d1w[w], 1);
+        d2w[w] |= __shfl_xor_sync(0xffffffffu, d2w[w], 1);
+    }
+    if ((lane & 1) == 0) {
+        *reinterpret_cast<uint2 *>(rec + s * 32 + i * 8) = make_uint2(d1w[0], d1w[1]);
+        *reinterpret_cast<uint2 *>(rec + 128 + s * 32 + i * 8) = make_uint2(d2w[0], d2w[1]);
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if ((kl & 31) == 0) s_sum[kl >> 5] = sum;
-    __syncthreads();
-    if (kl == 0) {
-        const int tot = s_sum[0] + s_sum[1] + s_sum[2] + s_sum[3];
+    if (lane == 0) {
         // a block that holds a NaN or an infinity poisons the token's outputs, as the plain arithmetic would
-        esc[blk * M + m] = any_bad ? __int_as_float(0x7fc00000) : e_scale;
-        xs[blk * M + m] = e_scale * static_cast<float>(tot);  // |tot| < 2^21: exact
+        esc[blk * M + m] = bad ? __int_as_float(0x7fc00000) : e_scale;
+        xs[blk * M + m] = e_scale * static_cast<float>(sum);  // |sum| < 2^21: exact
     }
 }
 
@@ -847,8 +863,8 @@ int launch_gemv_t(const uint8_t *packed, const void *x, int64_t ld_x, const void
     int8_t *xd = reinterpret_cast<int8_t *>(ws + kPCounterBytes + pl.slots_bytes);
     float *esc = reinterpret_cast<float *>(ws + kPCounterBytes + pl.slots_bytes + pl.xd_bytes);
     float *xs = reinterpret_cast<float *>(ws + kPCounterBytes + pl.slots_bytes + pl.xd_bytes + pl.tab_bytes);
-    w4a16_gemv_digits_kernel<T><<<dim3(static_cast<unsigned>(pl.nblocks), static_cast<unsigned>(M)), 128, 0, stream>>>(
-        static_cast<const T *>(x), ld_x, static_cast<int>(M), K, xd, esc, xs);
+    w4a16_gemv_digits_kernel<T><<<dim3(static_cast<unsigned>((pl.nblocks + 3) / 4), static_cast<unsigned>(M)), 128, 0,
+                                  stream>>>(static_cast<const T *>(x), ld_x, static_cast<int>(M), K, pl.nblocks, xd, esc, xs);
     QMM_CUDA_OK(cudaGetLastError());
     GvParams p;
     p.packed = packed;
