@@ -83,6 +83,22 @@ def test_against_oracle(capi, oracle, dev, shape, dtype):
         _assert_close(y, y_ref, rss, dtype)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(1, 256, 64, 128), (2, 384, 200, 128), (2, 8192, 1024, 256), (1, 4096, 7168, 128),
+                                   (2, 1024, 4096, 1024)])
+def test_one_or_two_tokens_meet_the_stock_tolerance(capi, oracle, dev, shape, dtype):
+    """One or two tokens take the integer dot-product kernel, which never rounds a weight: it meets the bound of
+    the stock-layout kernels, |y - y_ref| <= 2 u |y_ref| + 2^-7 (u / 2^-9) rms(row), not only the rss bound."""
+    M, K, N, group = shape
+    x, packed_w, scale, offset = oracle.make_w4a16_inputs(M, K, N, seed=M + K + N, group=group, dtype=dtype)
+    y_ref = oracle.weight_quant_batchmatmul(x, packed_w, scale, offset, antiquant_group_size=group)
+    buf = capi.w4a16_prepack(packed_w.to(dev), scale.to(dev), offset.to(dev), group_size=group)
+    y = capi.weight_quant_batchmatmul_prepacked(x.to(dev), buf, N).float().cpu().numpy()
+    u = 2.0 ** -9 if dtype == torch.bfloat16 else 2.0 ** -12
+    rms = np.sqrt(np.mean(y_ref ** 2, axis=1, keepdims=True))
+    assert np.all(np.abs(y - y_ref) <= 2 * u * np.abs(y_ref) + 2.0 ** -7 * (u / 2.0 ** -9) * rms + 1e-30)
+
+
 def test_bias_and_no_offset(capi, oracle, dev):
     x, packed_w, scale, _ = oracle.make_w4a16_inputs(5, 512, 256, seed=3)
     bias = torch.randn(256).to(torch.bfloat16)
