@@ -122,7 +122,7 @@ int launch_dynamic_quant(const T *x, int64_t rows, int64_t cols, int64_t ld_x, i
         while (tpr < 512 && tpr * 8 < nvec) tpr <<= 1;
         const int need = (nvec + tpr - 1) / tpr;
         const int vpt = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
-        const int threads = tpr > 256 ? tpr : 256;
+        const int threads = tpr > 128 ? tpr : 128;  // small CTAs: the tail of the grid is one CTA long
         const int rows_per_cta = threads / tpr;
         const int64_t grid = (rows + rows_per_cta - 1) / rows_per_cta;
         const int icols = static_cast<int>(cols);
